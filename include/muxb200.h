@@ -1,0 +1,268 @@
+/*
+ * muxb200 — C ABI of the B200 (sm_100a) paged decode attention path for
+ * MuxServe's FlexStore head-granular unified KV pool.
+ *
+ * Plain pointers, sizes and strides only: no torch types, no exceptions.
+ * Every entry point validates its arguments on the host and returns 0 or a
+ * negative mux_status_t BEFORE anything is launched; kernels are enqueued on
+ * the stream the caller passes and never synchronise the host.
+ *
+ * Pool geometry (muxserve/flexstore/manager.py:456-468 in the reference):
+ *   key pool    [num_blocks][head_size/x][block_size][x]   x = 16 / sizeof(elem)
+ *   value pool  [num_blocks][head_size][block_size]
+ * A block holds block_size tokens of ONE head of ONE layer of ONE model; the
+ * pool has no layer and no head dimension.  head_size is 128.
+ */
+#ifndef MUXB200_H_
+#define MUXB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  MUX_OK = 0,
+  MUX_ERR_NULL_POINTER = -1,
+  MUX_ERR_BAD_DTYPE = -2,
+  MUX_ERR_BAD_HEAD_SIZE = -3,     /* only 128 (muxserve/flexstore/manager.py:336-337) */
+  MUX_ERR_BAD_BLOCK_SIZE = -4,    /* only 8, 16, 32 (muxserve/arg_utils.py:61-65) */
+  MUX_ERR_MISALIGNED = -5,        /* a pointer or stride breaks the 16-byte rule */
+  MUX_ERR_BAD_SHAPE = -6,         /* negative / inconsistent sizes */
+  MUX_ERR_BAD_GROUP = -7,         /* q heads not a multiple of kv heads, or group too large */
+  MUX_ERR_WORKSPACE_TOO_SMALL = -8,
+  MUX_ERR_CUDA = -9,              /* a CUDA runtime call failed; see mux_last_cuda_error */
+  MUX_ERR_BAD_HANDLE = -10,
+  MUX_ERR_BUFFER_TOO_SMALL = -11,
+  MUX_ERR_UNKNOWN_REQUEST = -12,
+  MUX_ERR_TOO_LARGE = -13         /* beyond a stated fixed capacity */
+} mux_status_t;
+
+typedef enum { MUX_DTYPE_F16 = 0, MUX_DTYPE_BF16 = 1 } mux_dtype_t;
+
+/* Bits of the device status word (mux_device_status). */
+#define MUX_DEV_BAD_BLOCK_ID 1u   /* a block id outside [0, num_blocks) was met and replaced by 0 */
+#define MUX_DEV_WAIT_TIMEOUT 2u   /* a bounded wait on a staged copy ran out */
+#define MUX_DEV_BAD_CONTEXT 4u    /* a context length above max_context_len (or < 0) was met */
+#define MUX_DEV_BAD_SLOT 8u       /* a slot outside the pool was met and skipped */
+
+const char* mux_strerror(int status);
+/* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
+int mux_last_cuda_error(void);
+/* Library ABI version (bumped when a struct below changes). */
+int mux_abi_version(void);
+
+/* ------------------------------------------------------------------------
+ * reshape_and_cache — append new tokens' K/V rows to the pool.
+ *
+ * Replaces the MuxServe-vLLM fork's cache op reached from
+ * muxserve/flexserver/models/llama.py:160-161 (PagedAttentionWithRoPE) with
+ * slots produced by csrc/batch_scheduler.h:42-67:
+ *   s = slot_mapping[t, h];  b = s / block_size;  o = s % block_size
+ *   key_pool  [b][d / x][o][d % x] = k[t, h, d]
+ *   value_pool[b][d][o]            = v[t, h, d]
+ * A negative slot skips the row.  k and v may be strided views of a fused
+ * qkv tensor (llama.py:157-158): strides are in elements.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* k;               /* [num_tokens, num_kv_heads, head_size] */
+  const void* v;
+  int64_t k_token_stride;      /* elements between tokens */
+  int64_t k_head_stride;       /* elements between heads (normally head_size) */
+  int64_t v_token_stride;
+  int64_t v_head_stride;
+  void* key_cache;
+  void* value_cache;
+  int64_t num_blocks;          /* pool size in blocks */
+  const int64_t* slot_mapping; /* slot of (token t, head h) at [t*slot_token_stride + h*slot_head_stride] */
+  int64_t slot_token_stride;   /* elements; L*H for the reference's [T, L, H] tensor sliced at one layer */
+  int64_t slot_head_stride;    /* elements; 1 for that slice */
+  int32_t num_tokens;
+  int32_t num_kv_heads;
+  int32_t head_size;
+  int32_t block_size;
+  int32_t dtype;               /* mux_dtype_t */
+  int32_t reserved;
+} mux_cache_write_args_t;
+
+int mux_reshape_and_cache(const mux_cache_write_args_t* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------
+ * paged_attention — decode attention of one new query token per sequence
+ * over block-table-indirected KV blocks.
+ *
+ * Replaces the fork's attention op reached from llama.py:160-161; argument
+ * meaning follows paged_attention(out, q, key_cache, value_cache,
+ * head_mapping, scale, block_tables, context_lens, block_size,
+ * max_context_len).  In MuxServe mode block_tables for one layer is
+ * [num_seqs, num_kv_heads, max_blocks] (muxserve/flexserver/llm_runtime.py:327):
+ * every (sequence, kv head) has its own block list.
+ *   out[s, hq, :] = softmax_j(scale * q[s, hq, :] . K_j) . V_j ,  j < context_lens[s]
+ * with kv head h = head_mapping[hq] (NULL = hq / (num_q_heads/num_kv_heads)).
+ * Entries of a block list at or beyond ceil(context_len / block_size) are
+ * never read (the reference leaves them uninitialised).
+ *
+ * Long contexts are split into partitions of partition_size tokens that are
+ * combined through the caller's workspace (flash-decoding).  Sizes come from
+ * mux_paged_attention_workspace_size; workspace may be NULL when that is 0.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  void* out;                   /* [num_seqs, num_q_heads, head_size] */
+  const void* q;
+  int64_t q_seq_stride;        /* elements between sequences */
+  int64_t q_head_stride;       /* elements between q heads (normally head_size) */
+  int64_t out_seq_stride;
+  int64_t out_head_stride;
+  const void* key_cache;
+  const void* value_cache;
+  int64_t num_blocks;
+  const int32_t* head_mapping; /* [num_q_heads] device, or NULL for contiguous groups */
+  const int32_t* block_tables; /* device */
+  int64_t bt_seq_stride;       /* elements */
+  int64_t bt_head_stride;      /* elements; 0 = all kv heads share one list (plain vLLM layout) */
+  const int32_t* context_lens; /* [num_seqs] device */
+  float scale;
+  int32_t num_seqs;
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_size;
+  int32_t block_size;
+  int32_t max_context_len;
+  int32_t dtype;               /* mux_dtype_t */
+  int32_t partition_size;      /* tokens, multiple of block_size; 0 = library heuristic */
+  int32_t num_stages;          /* depth of the shared-memory block ring (multiple of 4, <= 16); 0 = default */
+} mux_attn_args_t;
+
+size_t mux_paged_attention_workspace_size(const mux_attn_args_t* args);
+int mux_paged_attention(const mux_attn_args_t* args, void* workspace,
+                        size_t workspace_bytes, void* cuda_stream);
+
+/* ------------------------------------------------------------------------
+ * paged_attention, mixed-model form — ONE launch serves the decode batches
+ * of several colocated models that share the pool.  No counterpart in the
+ * reference, which runs each model in its own processes
+ * (muxserve/muxsched/scheduler.py:167-208); the per-item fields restate what
+ * the single-model call derives from (sequence, kv head).
+ *
+ * An item is one (sequence, kv head) pair of some model:
+ *   q rows  [item_q_row[i], item_q_row[i] + item_group[i])  of the packed
+ *   q / out matrices [total_q_rows, head_size] attend over the block list
+ *   block_tables[i, :] with context length item_context_len[i] and softmax
+ *   scale item_scale[i].
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  void* out;                     /* packed [total_q_rows, head_size] */
+  const void* q;
+  int64_t q_row_stride;          /* elements (normally head_size) */
+  int64_t out_row_stride;
+  const void* key_cache;
+  const void* value_cache;
+  int64_t num_blocks;
+  const int32_t* block_tables;   /* [num_items, max_blocks] device */
+  int64_t bt_item_stride;        /* elements */
+  const int32_t* item_context_len; /* [num_items] device */
+  const int32_t* item_q_row;     /* [num_items] device */
+  const int32_t* item_group;     /* [num_items] device, each in [1, max_group] */
+  const float* item_scale;       /* [num_items] device */
+  int32_t num_items;
+  int32_t max_group;             /* upper bound of item_group, <= 8 */
+  int32_t head_size;
+  int32_t block_size;
+  int32_t max_context_len;
+  int32_t dtype;
+  int32_t partition_size;
+  int32_t num_stages;
+} mux_attn_mixed_args_t;
+
+size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* args);
+int mux_paged_attention_mixed(const mux_attn_mixed_args_t* args, void* workspace,
+                              size_t workspace_bytes, void* cuda_stream);
+
+/* Reads and clears the device status word (MUX_DEV_* bits) of the current
+ * device.  Synchronises the given stream. Returns a negative mux_status_t on failure. */
+int mux_device_status(void* cuda_stream);
+
+/* ------------------------------------------------------------------------
+ * Host side: block allocator.  Same observable behaviour as KVStorage in the
+ * reference (csrc/memory_manager.cpp:4-157): block ids, free-list order,
+ * preemption index, return encodings and counters.
+ * ---------------------------------------------------------------------- */
+typedef struct mux_kv_storage mux_kv_storage_t;
+
+mux_kv_storage_t* mux_kv_storage_create(int32_t num_blocks);        /* memory_manager.cpp:4-10 */
+void mux_kv_storage_destroy(mux_kv_storage_t* s);
+/* memory_manager.cpp:12-23.  Pops `size` ids from the tail of the free list. */
+int mux_kv_storage_allocate(mux_kv_storage_t* s, int32_t size, int32_t* out_ids);
+/* memory_manager.cpp:25-142.  alloc_info = rows [request id, logical blocks, has_blocks];
+ * writes [preempt_idx, block ids...] to out and its length to *out_len.  Call with
+ * out == NULL to learn the length that the same call would write WITHOUT changing state. */
+int mux_kv_storage_allocate_batch(mux_kv_storage_t* s, const int32_t* alloc_info,
+                                  int32_t num_requests, int32_t num_layers, int32_t num_heads,
+                                  int32_t* out, int64_t out_capacity, int64_t* out_len);
+/* memory_manager.cpp:144-157.  Returns the number of freed blocks (>= 0). */
+int64_t mux_kv_storage_free_batch(mux_kv_storage_t* s, const int32_t* request_ids, int32_t n);
+int32_t mux_kv_storage_new_blocks_allocated(const mux_kv_storage_t* s);  /* memory_manager.h:18 */
+int32_t mux_kv_storage_num_blocks_allocated(const mux_kv_storage_t* s);
+int64_t mux_kv_storage_num_free(const mux_kv_storage_t* s);
+/* Copies the free list (allocation order: the tail is handed out first). */
+int mux_kv_storage_free_list(const mux_kv_storage_t* s, int32_t* out, int64_t capacity);
+/* Invariant check: every id in [0,num_blocks) is in exactly one of free list / one owner. */
+int mux_kv_storage_check(const mux_kv_storage_t* s);
+
+/* ------------------------------------------------------------------------
+ * Host side: per-model step builder.  Same observable behaviour as
+ * BatchScheduler / Request in the reference (csrc/batch_scheduler.h:9-106,
+ * csrc/batch_scheduler.cpp:5-199), except that block-table padding, which the
+ * reference leaves uninitialised, is written as 0.
+ * ---------------------------------------------------------------------- */
+typedef struct mux_batch_scheduler mux_batch_scheduler_t;
+
+mux_batch_scheduler_t* mux_batch_scheduler_create(int32_t num_layers, int32_t num_heads,
+                                                  int32_t max_seq_len, int32_t block_size);
+void mux_batch_scheduler_destroy(mux_batch_scheduler_t* b);
+/* batch_scheduler.cpp:12-20 */
+int mux_batch_scheduler_add_request(mux_batch_scheduler_t* b, const int32_t* prompt,
+                                    int32_t prompt_len, int32_t req_id, int32_t max_tokens);
+/* batch_scheduler.cpp:22-48.  out has 3*n+1 entries. last_tokens may be NULL (prefill). */
+int mux_batch_scheduler_try_batch(mux_batch_scheduler_t* b, const int32_t* req_ids, int32_t n,
+                                  const int32_t* last_tokens, int32_t n_last, int32_t* out);
+/* batch_scheduler.cpp:51-97.  out receives [numTokens, numContexts, maxContextLen,
+ * maxBlocksPerSeq, L, H, prompt lens...]; *out_len its length. */
+int mux_batch_scheduler_get_batch_info(mux_batch_scheduler_t* b, const int32_t* block_request,
+                                       int32_t n, const int32_t* block_info, int64_t block_info_len,
+                                       int32_t* out, int32_t out_capacity, int32_t* out_len);
+/* batch_scheduler.cpp:99-193.  Buffers are host memory sized by the caller from
+ * get_batch_info, as muxserve/flexserver/llm_runtime.py:300-312 does:
+ *   tokens, positions [padded_len] int32;  context_lens [numContexts] int32;
+ *   block_tables [numTokens, maxBlocksPerSeq, L, H] int32;  slot_mapping [numTokens, L, H] int64. */
+int mux_batch_scheduler_get_batch(mux_batch_scheduler_t* b, const int32_t* block_request, int32_t n,
+                                  const int32_t* block_info, int64_t block_info_len,
+                                  int32_t* tokens, int32_t* positions, int32_t padded_len,
+                                  int32_t* context_lens, int32_t num_contexts,
+                                  int32_t* block_tables, int64_t block_tables_len,
+                                  int64_t* slot_mapping, int64_t slot_mapping_len);
+/* Same step as get_batch for a decode batch, but block tables are written in the
+ * layout the kernels consume, [L, numContexts, H, maxBlocksPerSeq], which the reference
+ * reaches by a device permute (llm_runtime.py:327). */
+int mux_batch_scheduler_get_batch_decode_layered(
+    mux_batch_scheduler_t* b, const int32_t* block_request, int32_t n,
+    const int32_t* block_info, int64_t block_info_len,
+    int32_t* tokens, int32_t* positions, int32_t padded_len,
+    int32_t* context_lens, int32_t num_contexts,
+    int32_t* block_tables, int64_t block_tables_len,
+    int64_t* slot_mapping, int64_t slot_mapping_len);
+int mux_batch_scheduler_release_requests(mux_batch_scheduler_t* b, const int32_t* req_ids, int32_t n);
+/* batch_scheduler.h:88-92.  Each copies up to capacity entries and returns the full length. */
+int32_t mux_batch_scheduler_preempt_requests(const mux_batch_scheduler_t* b, int32_t* out, int32_t capacity);
+int32_t mux_batch_scheduler_prompt_info(const mux_batch_scheduler_t* b, int32_t* out, int32_t capacity);
+/* pairs [request id, max tokens] */
+int32_t mux_batch_scheduler_batch_reqs(const mux_batch_scheduler_t* b, int32_t* out, int32_t capacity);
+/* Introspection for tests: [contextLen, numPhysicalBlocks, logicalBlockIdx, logicalBlockOffset, numOutputs]. */
+int mux_batch_scheduler_request_state(const mux_batch_scheduler_t* b, int32_t req_id, int32_t out[5]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUXB200_H_ */

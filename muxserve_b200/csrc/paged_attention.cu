@@ -1,0 +1,685 @@
+// Decode-phase paged attention over a head-granular unified KV pool (sm_100a).
+//
+// Work unit = one partition (<= partition_size tokens) of one (sequence, kv head)
+// item.  One CTA per unit: a producer warp walks the item's block list and
+// streams every 16-token K block and V block (head_size*block_size*2 bytes, one
+// contiguous piece of the pool) into a shared-memory ring with 1-D bulk (TMA)
+// copies completed on mbarriers; four consumer warps take the staged blocks in
+// turn.  The grouped query heads of the item (1 for MHA, up to 8 for GQA) form
+// the N=8 dimension of m16n8k16 tensor-core MMAs whose M dimension is the 16
+// tokens of a block: the pool's own layouts, K [d/8][token][8] and V [d][token],
+// are exactly the row-major A operands of K.Q^T and V^T.P^T, so the staged
+// bytes are used as they arrive.
+//
+//   phase 1  logits[h][t] = scale * K[t,:] . q[h,:]   for all K blocks of the unit
+//   softmax  over the unit (max, exp, sum) -> P in the KV dtype
+//   phase 2  out^T[d][h] += V^T[d,t] P^T[t,h]         for all V blocks of the unit
+//
+// A unit that covers its whole context writes `out`; otherwise it writes an
+// un-normalised fp32 partial (acc, max, sum) to the workspace and a second
+// small kernel merges the partitions (flash-decoding).
+#include <algorithm>
+#include <cstdint>
+
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace mux {
+
+constexpr int kHeadSize = 128;
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;  // + producer warp
+constexpr int kMaxStages = 16;
+constexpr int kRedStride = kHeadSize + 4;  // padded row of the cross-warp reduction
+constexpr int kMaxSmemBytes = 227 * 1024;
+constexpr int kMaxDevicesTracked = 64;
+
+struct AttnParams {
+  const void* q;
+  void* out;
+  const void* kc;
+  const void* vc;
+  const int* block_tables;
+  const int* context_lens;
+  const int* head_mapping;
+  const int* item_ctx;
+  const int* item_q_row;
+  const int* item_group;
+  const float* item_scale;
+  long long q_s0, q_s1, o_s0, o_s1;  // single model: seq, head strides; mixed: s1 = row stride
+  long long bt_s0, bt_s1;            // single model: seq, head strides; mixed: s0 = item stride
+  float* ws_acc;
+  float* ws_ml;
+  unsigned* status;
+  long long num_blocks;
+  float scale;
+  int num_q_heads, num_kv_heads, group;
+  int gs;          // head columns kept in shared memory (1..8)
+  int head_tiles;  // ceil(group / 8)
+  int pb;          // partition size in blocks
+  int max_parts;
+  int max_context_len;
+  int nst;         // ring depth in tiles
+};
+
+// Shared-memory carve-up, identical on host (sizing) and device.
+struct SmemLayout {
+  int ring, s, pm, ids, info, bars, total;
+  int srow, prow;
+};
+
+__host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs, int nst) {
+  SmemLayout L;
+  const int tile = kHeadSize * block_size * 2;
+  const int P = pb * block_size;
+  L.srow = P + 8;
+  L.prow = P + 16;
+  int off = 0;
+  L.ring = off;
+  off += nst * tile;
+  L.s = off;
+  int s_bytes = gs * L.srow * 4;
+  int red_bytes = kConsumerWarps * gs * kRedStride * 4;
+  off += (s_bytes > red_bytes ? s_bytes : red_bytes);
+  off = (off + 15) & ~15;
+  L.pm = off;
+  off += gs * L.prow * 2;
+  off = (off + 15) & ~15;
+  L.ids = off;
+  off += pb * 4;
+  off = (off + 15) & ~15;
+  L.info = off;
+  off += 8 * 8 + 8 * 8 + 8 * 2 * 4 + 16;  // qoff, ooff, ml, geff
+  L.bars = off;
+  off += 2 * kMaxStages * 8;
+  L.total = off;
+  return L;
+}
+
+struct ItemInfo {
+  long long qoff[8];
+  long long ooff[8];
+  float ml[8][2];
+  int geff;
+  int pad[3];
+};
+
+struct ItemDesc {
+  int ctx, G, seq, kvh;
+  float scale;
+  const int* bt_row;
+};
+
+template <bool MIXED>
+__device__ __forceinline__ ItemDesc load_item(const AttnParams& p, int item) {
+  ItemDesc d;
+  if (MIXED) {
+    d.ctx = p.item_ctx[item];
+    d.G = p.item_group[item];
+    d.scale = p.item_scale[item];
+    d.bt_row = p.block_tables + (long long)item * p.bt_s0;
+    d.seq = 0;
+    d.kvh = 0;
+  } else {
+    d.seq = item / p.num_kv_heads;
+    d.kvh = item - d.seq * p.num_kv_heads;
+    d.ctx = p.context_lens[d.seq];
+    d.G = p.group;
+    d.scale = p.scale;
+    d.bt_row = p.block_tables + (long long)d.seq * p.bt_s0 + (long long)d.kvh * p.bt_s1;
+  }
+  return d;
+}
+
+// Executed by one full warp: element offsets of the (up to 8) q / out rows of
+// this head tile, and how many of them exist.
+template <bool MIXED>
+__device__ __forceinline__ void resolve_heads(const AttnParams& p, const ItemDesc& d, int item,
+                                              int htile, ItemInfo* info, int lane) {
+  if (MIXED) {
+    if (lane < 8) {
+      long long row = (long long)p.item_q_row[item] + htile * 8 + lane;
+      info->qoff[lane] = row * p.q_s1;
+      info->ooff[lane] = row * p.o_s1;
+    }
+    if (lane == 0) info->geff = max(0, min(8, d.G - htile * 8));
+  } else if (p.head_mapping == nullptr) {
+    if (lane < 8) {
+      long long hq = (long long)d.kvh * d.G + htile * 8 + lane;
+      info->qoff[lane] = (long long)d.seq * p.q_s0 + hq * p.q_s1;
+      info->ooff[lane] = (long long)d.seq * p.o_s0 + hq * p.o_s1;
+    }
+    if (lane == 0) info->geff = max(0, min(8, d.G - htile * 8));
+  } else {
+    // General head_mapping: ordered compaction of the q heads mapped to this kv head.
+    int count = 0;
+    for (int base = 0; base < p.num_q_heads; base += 32) {
+      int hq = base + lane;
+      bool match = hq < p.num_q_heads && p.head_mapping[hq] == d.kvh;
+      unsigned bal = __ballot_sync(0xffffffffu, match);
+      int pos = count + __popc(bal & ((1u << lane) - 1u)) - htile * 8;
+      if (match && pos >= 0 && pos < 8) {
+        info->qoff[pos] = (long long)d.seq * p.q_s0 + (long long)hq * p.q_s1;
+        info->ooff[pos] = (long long)d.seq * p.o_s0 + (long long)hq * p.o_s1;
+      }
+      count += __popc(bal);
+    }
+    if (lane == 0) {
+      if (count != d.G) atomicOr(p.status, MUX_DEV_BAD_HEAD_MAPPING);
+      info->geff = max(0, min(8, count - htile * 8));
+    }
+  }
+}
+
+template <typename T, int BS, bool MIXED>
+__global__ void __launch_bounds__(kThreads)
+paged_attn_kernel(const __grid_constant__ AttnParams p) {
+  constexpr int TILE = kHeadSize * BS * 2;       // bytes of one K or V block
+  constexpr int MT = BS >= 16 ? BS / 16 : 1;     // 16-token m-tiles per K block
+  constexpr int KSTEPS = BS >= 16 ? BS / 16 : 1; // 16-token k-steps per V block
+  constexpr int CHUNK = BS * 16;                 // bytes of one 8-wide d chunk row of K
+  constexpr int VROW = BS * 2;                   // bytes of one d row of V
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int item = blockIdx.x, part = blockIdx.y, htile = blockIdx.z;
+  const int P = p.pb * BS;
+
+  ItemDesc d = load_item<MIXED>(p, item);
+  if (d.ctx < 0 || d.ctx > p.max_context_len) {
+    if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
+    d.ctx = d.ctx < 0 ? 0 : p.max_context_len;
+  }
+  const int nparts = (d.ctx + P - 1) / P;
+  if (part >= nparts && !(d.ctx == 0 && part == 0)) return;
+
+  const SmemLayout L = smem_layout(BS, p.pb, p.gs, p.nst);
+  ItemInfo* info = reinterpret_cast<ItemInfo*>(smem + L.info);
+  const uint32_t bars = smem_u32(smem + L.bars);  // full[i] at +8i, empty[i] at +8(kMaxStages+i)
+  const int nst = p.nst;
+
+  if (warp == 0) resolve_heads<MIXED>(p, d, item, htile, info, lane);
+  if (tid == kConsumerThreads) {
+    for (int i = 0; i < nst; ++i) {
+      mbar_init(bars + 8 * i, 1);
+      mbar_init(bars + 8 * (kMaxStages + i), 1);
+    }
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  const int geff = info->geff;
+  if (geff <= 0) return;
+  T* out = static_cast<T*>(p.out);
+  if (d.ctx == 0) {  // empty context: defined output (zeros), nothing to attend to
+    if (tid < kHeadSize)
+      for (int n = 0; n < geff; ++n) out[info->ooff[n] + tid] = from_float<T>(0.f);
+    return;
+  }
+
+  const int tok0 = part * P;
+  const int ntok = min(d.ctx - tok0, P);
+  const int nblk = (ntok + BS - 1) / BS;
+  const uint32_t ring = smem_u32(smem + L.ring);
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer warp ----------------
+    int* ids = reinterpret_cast<int*>(smem + L.ids);
+    for (int i = lane; i < nblk; i += 32) {
+      int id = d.bt_row[part * p.pb + i];
+      if (id < 0 || id >= p.num_blocks) {
+        atomicOr(p.status, MUX_DEV_BAD_BLOCK_ID);
+        id = 0;
+      }
+      ids[i] = id;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
+      const unsigned char* vc = static_cast<const unsigned char*>(p.vc);
+      const int ntiles = 2 * nblk;
+      for (int j = 0; j < ntiles; ++j) {
+        const int stage = j % nst, use = j / nst;
+        if (use > 0)
+          mbar_wait(bars + 8 * (kMaxStages + stage), (use - 1) & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
+        const unsigned char* src = j < nblk ? kc + (long long)ids[j] * TILE
+                                            : vc + (long long)ids[j - nblk] * TILE;
+        mbar_arrive_expect_tx(bars + 8 * stage, TILE);
+        bulk_g2s(ring + stage * TILE, src, TILE, bars + 8 * stage);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  const int g = lane >> 2, tq = lane & 3;
+  float* S = reinterpret_cast<float*>(smem + L.s);
+  T* Pm = reinterpret_cast<T*>(smem + L.pm);
+  const int SROW = L.srow, PROW = L.prow;
+
+  // q as the B operand (k = d, n = head): b0 = q[g][16ks + 2tq, +1], b1 = q[g][16ks + 8 + 2tq, +1]
+  uint32_t qf[8][2];
+  {
+    const T* q = static_cast<const T*>(p.q);
+    if (g < geff) {
+      const T* qr = q + info->qoff[g];
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        qf[ks][0] = ldg32_nc(qr + ks * 16 + 2 * tq);
+        qf[ks][1] = ldg32_nc(qr + ks * 16 + 8 + 2 * tq);
+      }
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) qf[ks][0] = qf[ks][1] = 0u;
+    }
+  }
+
+  // ---- phase 1: logits ----
+  {
+    const int n0 = 2 * tq;
+    const int lm_tok = (lane & 7) + (BS >= 16 ? ((lane >> 3) & 1) * 8 : 0);
+    const int lm_chunk = lane >> 4;
+    for (int jb = warp; jb < nblk; jb += kConsumerWarps) {
+      const int stage = jb % nst, use = jb / nst;
+      mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
+      const uint32_t tile = ring + stage * TILE;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          uint32_t a[4];
+          ldmatrix_x4(a, tile + (2 * ks + lm_chunk) * CHUNK + (mt * 16 + lm_tok) * 16);
+          mma_16816<T>(c, a, qf[ks][0], qf[ks][1]);
+        }
+        const int tok = jb * BS + mt * 16 + g;
+        if (n0 < geff) {
+          S[n0 * SROW + tok] = c[0] * d.scale;
+          if (BS >= 16) S[n0 * SROW + tok + 8] = c[2] * d.scale;
+        }
+        if (n0 + 1 < geff) {
+          S[(n0 + 1) * SROW + tok] = c[1] * d.scale;
+          if (BS >= 16) S[(n0 + 1) * SROW + tok + 8] = c[3] * d.scale;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kMaxStages + stage));
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+
+  // ---- softmax over the unit ----
+  for (int n = warp; n < geff; n += kConsumerWarps) {
+    const float* srow = S + n * SROW;
+    float m = -INFINITY;
+    for (int t = lane; t < ntok; t += 32) m = fmaxf(m, srow[t]);
+    m = warp_max(m);
+    float l = 0.f;
+    T* prow = Pm + n * PROW;
+    for (int t = lane; t < nblk * BS; t += 32) {
+      float pv = t < ntok ? __expf(srow[t] - m) : 0.f;
+      l += pv;
+      prow[t] = from_float<T>(pv);
+    }
+    l = warp_sum(l);
+    if (lane == 0) {
+      info->ml[n][0] = m;
+      info->ml[n][1] = l;
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+
+  // ---- phase 2: out^T[d][h] = sum_t V^T[d][t] P^T[t][h] ----
+  float acc[8][4];
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+  {
+    const uint32_t pm_base = smem_u32(Pm);
+    const bool lane_has = (BS >= 16) || (tq < 2);
+    for (int jb = warp; jb < nblk; jb += kConsumerWarps) {
+      const int j = nblk + jb;
+      const int stage = j % nst, use = j / nst;
+      mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
+      const uint32_t tile = ring + stage * TILE;
+      const int rem = ntok - jb * BS;  // valid tokens of this block
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        // This lane's four tokens of the k-step: slots {2tq,2tq+1} and {8+2tq,9+2tq}
+        // of the MMA are tokens t0..t0+3 (same mapping in A and B).
+        const int t0 = ks * 16 + 4 * tq;
+        uint32_t b0 = 0u, b1 = 0u;
+        if (g < geff && lane_has) {
+          uint2 pv = lds64(pm_base + (g * PROW + jb * BS + t0) * 2);
+          b0 = pv.x;
+          b1 = pv.y;
+        }
+        uint32_t mlo = 0xffffffffu, mhi = 0xffffffffu;
+        if (rem < BS) {  // stale tail of the last block may hold anything, NaN included
+          mlo = (t0 < rem ? 0x0000ffffu : 0u) | (t0 + 1 < rem ? 0xffff0000u : 0u);
+          mhi = (t0 + 2 < rem ? 0x0000ffffu : 0u) | (t0 + 3 < rem ? 0xffff0000u : 0u);
+        }
+        if (!lane_has) mlo = mhi = 0u;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+          const int row = mt * 16 + g;
+          uint2 r0 = lds64(tile + row * VROW + t0 * 2);
+          uint2 r1 = lds64(tile + (row + 8) * VROW + t0 * 2);
+          uint32_t a[4] = {r0.x & mlo, r1.x & mlo, r0.y & mhi, r1.y & mhi};
+          mma_16816<T>(acc[mt], a, b0, b1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kMaxStages + stage));
+    }
+  }
+
+  // ---- cross-warp reduction (aliases the logits, which are dead by now) ----
+  float* red = S;
+  {
+    const int n0 = 2 * tq;
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      const int d0 = mt * 16 + g;
+      if (n0 < geff) {
+        red[(warp * p.gs + n0) * kRedStride + d0] = acc[mt][0];
+        red[(warp * p.gs + n0) * kRedStride + d0 + 8] = acc[mt][2];
+      }
+      if (n0 + 1 < geff) {
+        red[(warp * p.gs + n0 + 1) * kRedStride + d0] = acc[mt][1];
+        red[(warp * p.gs + n0 + 1) * kRedStride + d0 + 8] = acc[mt][3];
+      }
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+  {
+    const int dd = tid;  // 0..127
+    const long long slot = ((long long)item * p.head_tiles + htile) * p.max_parts + part;
+    for (int n = 0; n < geff; ++n) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) s += red[(w * p.gs + n) * kRedStride + dd];
+      if (nparts == 1) {
+        out[info->ooff[n] + dd] = from_float<T>(s / info->ml[n][1]);
+      } else {
+        p.ws_acc[(slot * p.gs + n) * kHeadSize + dd] = s;
+        if (dd == 0) {
+          p.ws_ml[(slot * p.gs + n) * 2] = info->ml[n][0];
+          p.ws_ml[(slot * p.gs + n) * 2 + 1] = info->ml[n][1];
+        }
+      }
+    }
+  }
+}
+
+// Merges the partitions of every item that has more than one.
+template <typename T, int BS, bool MIXED>
+__global__ void __launch_bounds__(kHeadSize)
+paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
+  __shared__ ItemInfo info;
+  const int item = blockIdx.x, htile = blockIdx.y;
+  const int tid = threadIdx.x;
+  const int P = p.pb * BS;
+  ItemDesc d = load_item<MIXED>(p, item);
+  if (d.ctx < 0) d.ctx = 0;
+  if (d.ctx > p.max_context_len) d.ctx = p.max_context_len;
+  const int nparts = (d.ctx + P - 1) / P;
+  if (nparts <= 1) return;
+  if (tid < 32) resolve_heads<MIXED>(p, d, item, htile, &info, tid);
+  __syncthreads();
+  const int geff = info.geff;
+  T* out = static_cast<T*>(p.out);
+  const long long slot0 = ((long long)item * p.head_tiles + htile) * p.max_parts;
+  for (int n = 0; n < geff; ++n) {
+    float M = -INFINITY;
+    for (int k = 0; k < nparts; ++k) M = fmaxf(M, p.ws_ml[((slot0 + k) * p.gs + n) * 2]);
+    float acc = 0.f, lsum = 0.f;
+    for (int k = 0; k < nparts; ++k) {
+      const long long r = (slot0 + k) * p.gs + n;
+      const float w = __expf(p.ws_ml[r * 2] - M);
+      lsum += p.ws_ml[r * 2 + 1] * w;
+      acc += p.ws_acc[r * kHeadSize + tid] * w;
+    }
+    out[info.ooff[n] + tid] = from_float<T>(acc / lsum);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+struct Plan {
+  int pb, max_parts, gs, head_tiles, nst, smem;
+  size_t ws_acc_bytes, ws_ml_bytes;
+};
+
+static int default_stages(int block_size) {
+  // 32 KiB of staged blocks per CTA.
+  int tile = kHeadSize * block_size * 2;
+  int n = (32 * 1024) / tile;
+  return std::max(kConsumerWarps, std::min(kMaxStages, n));
+}
+
+static Plan make_plan(long long items, int group, int block_size, int max_context_len,
+                      int partition_size, int num_stages) {
+  Plan pl;
+  int psize = partition_size > 0 ? partition_size : 256;
+  psize = std::max(block_size, (psize / block_size) * block_size);
+  pl.pb = psize / block_size;
+  pl.max_parts = std::max(1, (max_context_len + psize - 1) / psize);
+  pl.gs = std::min(8, std::max(1, group));
+  pl.head_tiles = (std::max(1, group) + 7) / 8;
+  // The ring depth must be a multiple of the consumer-warp count: then every
+  // stage is always consumed by the same warp, whose mbarrier parity waits are
+  // therefore never more than one phase apart.
+  pl.nst = num_stages > 0 ? num_stages : default_stages(block_size);
+  pl.nst = std::min(kMaxStages, std::max(kConsumerWarps, (pl.nst / kConsumerWarps) * kConsumerWarps));
+  pl.smem = smem_layout(block_size, pl.pb, pl.gs, pl.nst).total;
+  if (pl.max_parts > 1) {
+    size_t slots = (size_t)items * pl.head_tiles * pl.max_parts * pl.gs;
+    pl.ws_acc_bytes = slots * kHeadSize * sizeof(float);
+    pl.ws_ml_bytes = slots * 2 * sizeof(float);
+  } else {
+    pl.ws_acc_bytes = pl.ws_ml_bytes = 0;
+  }
+  return pl;
+}
+
+template <typename T, int BS, bool MIXED>
+static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream) {
+  auto kern = paged_attn_kernel<T, BS, MIXED>;
+  if (pl.smem > kMaxSmemBytes) return MUX_ERR_BAD_SHAPE;  // partition too large for one SM
+  static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (dev < 0 || dev >= kMaxDevicesTracked || granted[dev] < pl.smem) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev >= 0 && dev < kMaxDevicesTracked) granted[dev] = pl.smem;
+  }
+  dim3 grid((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
+  kern<<<grid, kThreads, pl.smem, stream>>>(prm);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (pl.max_parts > 1) {
+    dim3 mgrid((unsigned)items, (unsigned)pl.head_tiles);
+    paged_attn_merge_kernel<T, BS, MIXED><<<mgrid, kHeadSize, 0, stream>>>(prm);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
+  return MUX_OK;
+}
+
+template <bool MIXED>
+static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, int block_size,
+                  cudaStream_t stream) {
+#define MUX_CASE(T, BS) return launch_typed<T, BS, MIXED>(prm, pl, items, stream)
+  if (dtype == MUX_DTYPE_F16) {
+    if (block_size == 8) MUX_CASE(__half, 8);
+    if (block_size == 16) MUX_CASE(__half, 16);
+    MUX_CASE(__half, 32);
+  } else {
+    if (block_size == 8) MUX_CASE(__nv_bfloat16, 8);
+    if (block_size == 16) MUX_CASE(__nv_bfloat16, 16);
+    MUX_CASE(__nv_bfloat16, 32);
+  }
+#undef MUX_CASE
+}
+
+static int check_common(int dtype, int head_size, int block_size) {
+  if (dtype != MUX_DTYPE_F16 && dtype != MUX_DTYPE_BF16) return MUX_ERR_BAD_DTYPE;
+  if (head_size != kHeadSize) return MUX_ERR_BAD_HEAD_SIZE;
+  if (block_size != 8 && block_size != 16 && block_size != 32) return MUX_ERR_BAD_BLOCK_SIZE;
+  return MUX_OK;
+}
+
+static int validate(const mux_attn_args_t* a) {
+  if (a == nullptr) return MUX_ERR_NULL_POINTER;
+  int st = check_common(a->dtype, a->head_size, a->block_size);
+  if (st != MUX_OK) return st;
+  if (a->num_seqs < 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->max_context_len < 0 ||
+      a->num_blocks <= 0 || a->partition_size < 0 || a->num_stages < 0)
+    return MUX_ERR_BAD_SHAPE;
+  if (a->partition_size % a->block_size != 0) return MUX_ERR_BAD_SHAPE;
+  if (a->num_q_heads % a->num_kv_heads != 0) return MUX_ERR_BAD_GROUP;
+  if (a->num_seqs == 0) return MUX_OK;
+  if (!a->out || !a->q || !a->key_cache || !a->value_cache || !a->block_tables || !a->context_lens)
+    return MUX_ERR_NULL_POINTER;
+  if (!aligned16(a->key_cache) || !aligned16(a->value_cache) || !aligned16(a->q) || !aligned16(a->out))
+    return MUX_ERR_MISALIGNED;
+  // q rows are read as 32-bit pairs, out rows written per element: 4-byte rule on strides.
+  if ((a->q_seq_stride & 1) || (a->q_head_stride & 1)) return MUX_ERR_MISALIGNED;
+  if (a->bt_seq_stride < 0 || a->bt_head_stride < 0) return MUX_ERR_BAD_SHAPE;
+  return MUX_OK;
+}
+
+static int validate(const mux_attn_mixed_args_t* a) {
+  if (a == nullptr) return MUX_ERR_NULL_POINTER;
+  int st = check_common(a->dtype, a->head_size, a->block_size);
+  if (st != MUX_OK) return st;
+  if (a->num_items < 0 || a->max_context_len < 0 || a->num_blocks <= 0 || a->partition_size < 0 ||
+      a->num_stages < 0)
+    return MUX_ERR_BAD_SHAPE;
+  if (a->partition_size % a->block_size != 0) return MUX_ERR_BAD_SHAPE;
+  if (a->max_group < 1 || a->max_group > 8) return MUX_ERR_BAD_GROUP;
+  if (a->num_items == 0) return MUX_OK;
+  if (!a->out || !a->q || !a->key_cache || !a->value_cache || !a->block_tables ||
+      !a->item_context_len || !a->item_q_row || !a->item_group || !a->item_scale)
+    return MUX_ERR_NULL_POINTER;
+  if (!aligned16(a->key_cache) || !aligned16(a->value_cache) || !aligned16(a->q) || !aligned16(a->out))
+    return MUX_ERR_MISALIGNED;
+  if (a->q_row_stride & 1) return MUX_ERR_MISALIGNED;
+  if (a->bt_item_stride < 0) return MUX_ERR_BAD_SHAPE;
+  return MUX_OK;
+}
+
+}  // namespace mux
+
+extern "C" {
+
+size_t mux_paged_attention_workspace_size(const mux_attn_args_t* a) {
+  if (mux::validate(a) != MUX_OK || a->num_seqs == 0) return 0;
+  mux::Plan pl = mux::make_plan((long long)a->num_seqs * a->num_kv_heads,
+                                a->num_q_heads / a->num_kv_heads, a->block_size,
+                                a->max_context_len, a->partition_size, a->num_stages);
+  return pl.ws_acc_bytes + pl.ws_ml_bytes;
+}
+
+int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t workspace_bytes,
+                        void* cuda_stream) {
+  int st = mux::validate(a);
+  if (st != MUX_OK) return st;
+  if (a->num_seqs == 0) return MUX_OK;
+  const long long items = (long long)a->num_seqs * a->num_kv_heads;
+  const int group = a->num_q_heads / a->num_kv_heads;
+  mux::Plan pl = mux::make_plan(items, group, a->block_size, a->max_context_len,
+                                a->partition_size, a->num_stages);
+  const size_t need = pl.ws_acc_bytes + pl.ws_ml_bytes;
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return MUX_ERR_WORKSPACE_TOO_SMALL;
+  if (need > 0 && !mux::aligned16(workspace)) return MUX_ERR_MISALIGNED;
+  if (items > 0x7fffffffLL || pl.max_parts > 65535) return MUX_ERR_BAD_SHAPE;
+  unsigned* status = mux::device_status_ptr();
+  if (status == nullptr) return MUX_ERR_CUDA;
+
+  mux::AttnParams prm = {};
+  prm.q = a->q;
+  prm.out = a->out;
+  prm.kc = a->key_cache;
+  prm.vc = a->value_cache;
+  prm.block_tables = a->block_tables;
+  prm.context_lens = a->context_lens;
+  prm.head_mapping = a->head_mapping;
+  prm.q_s0 = a->q_seq_stride;
+  prm.q_s1 = a->q_head_stride;
+  prm.o_s0 = a->out_seq_stride;
+  prm.o_s1 = a->out_head_stride;
+  prm.bt_s0 = a->bt_seq_stride;
+  prm.bt_s1 = a->bt_head_stride;
+  prm.ws_acc = static_cast<float*>(workspace);
+  prm.ws_ml = need > 0 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.ws_acc_bytes)
+                       : nullptr;
+  prm.status = status;
+  prm.num_blocks = a->num_blocks;
+  prm.scale = a->scale;
+  prm.num_q_heads = a->num_q_heads;
+  prm.num_kv_heads = a->num_kv_heads;
+  prm.group = group;
+  prm.gs = pl.gs;
+  prm.head_tiles = pl.head_tiles;
+  prm.pb = pl.pb;
+  prm.max_parts = pl.max_parts;
+  prm.max_context_len = a->max_context_len;
+  prm.nst = pl.nst;
+  return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
+                            static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* a) {
+  if (mux::validate(a) != MUX_OK || a->num_items == 0) return 0;
+  mux::Plan pl = mux::make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len,
+                                a->partition_size, a->num_stages);
+  return pl.ws_acc_bytes + pl.ws_ml_bytes;
+}
+
+int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
+                              size_t workspace_bytes, void* cuda_stream) {
+  int st = mux::validate(a);
+  if (st != MUX_OK) return st;
+  if (a->num_items == 0) return MUX_OK;
+  mux::Plan pl = mux::make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len,
+                                a->partition_size, a->num_stages);
+  const size_t need = pl.ws_acc_bytes + pl.ws_ml_bytes;
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return MUX_ERR_WORKSPACE_TOO_SMALL;
+  if (need > 0 && !mux::aligned16(workspace)) return MUX_ERR_MISALIGNED;
+  if (pl.max_parts > 65535) return MUX_ERR_BAD_SHAPE;
+  unsigned* status = mux::device_status_ptr();
+  if (status == nullptr) return MUX_ERR_CUDA;
+
+  mux::AttnParams prm = {};
+  prm.q = a->q;
+  prm.out = a->out;
+  prm.kc = a->key_cache;
+  prm.vc = a->value_cache;
+  prm.block_tables = a->block_tables;
+  prm.item_ctx = a->item_context_len;
+  prm.item_q_row = a->item_q_row;
+  prm.item_group = a->item_group;
+  prm.item_scale = a->item_scale;
+  prm.q_s1 = a->q_row_stride;
+  prm.o_s1 = a->out_row_stride;
+  prm.bt_s0 = a->bt_item_stride;
+  prm.ws_acc = static_cast<float*>(workspace);
+  prm.ws_ml = need > 0 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.ws_acc_bytes)
+                       : nullptr;
+  prm.status = status;
+  prm.num_blocks = a->num_blocks;
+  prm.gs = pl.gs;
+  prm.head_tiles = 1;
+  prm.pb = pl.pb;
+  prm.max_parts = pl.max_parts;
+  prm.max_context_len = a->max_context_len;
+  prm.nst = pl.nst;
+  return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
+                           static_cast<cudaStream_t>(cuda_stream));
+}
+
+}  // extern "C"

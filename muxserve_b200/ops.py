@@ -1,0 +1,247 @@
+"""The two operators of the decode attention path, with the reference's signatures.
+
+``reshape_and_cache`` and ``paged_attention`` take the arguments of the ops that
+MuxServe's ``PagedAttentionWithRoPE`` layer calls
+(muxserve/flexserver/models/llama.py:138-147,160-161; the op source lives in the
+un-vendored MuxServe-vLLM fork).  ``paged_attention_mixed`` is the extension
+that serves several colocated models in one launch.  All three go through the
+C ABI in ``libmuxb200.so`` on the current CUDA stream; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import AttnArgs, AttnMixedArgs, CacheWriteArgs, check, lib
+
+HEAD_SIZE = 128
+
+_DTYPES = {torch.float16: _lib.MUX_DTYPE_F16, torch.bfloat16: _lib.MUX_DTYPE_BF16}
+_workspaces = {}
+
+
+def _dtype_code(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"{name} must be float16 or bfloat16, got {t.dtype}")
+    return _DTYPES[t.dtype]
+
+
+def _require_cuda(**tensors) -> torch.device:
+    dev = None
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor (this op has no CPU implementation)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"{name} is on {t.device}, expected {dev}")
+    return dev
+
+
+def _rows(t: torch.Tensor, name: str):
+    """Views [N, H*D] or [N, H, D] as (N, H, row stride, head stride); last dim must be dense."""
+    if t.dim() == 2:
+        if t.shape[1] % HEAD_SIZE != 0 or (t.shape[1] > 0 and t.stride(1) != 1):
+            raise ValueError(f"{name}: expected [N, heads*{HEAD_SIZE}] with a dense last dim")
+        return t.shape[0], t.shape[1] // HEAD_SIZE, t.stride(0), HEAD_SIZE
+    if t.dim() == 3:
+        if t.shape[2] != HEAD_SIZE or t.stride(2) != 1:
+            raise ValueError(f"{name}: expected [N, heads, {HEAD_SIZE}] with a dense last dim")
+        return t.shape[0], t.shape[1], t.stride(0), t.stride(1)
+    raise ValueError(f"{name}: expected a 2-D or 3-D tensor")
+
+
+def _pool(key_cache: torch.Tensor, value_cache: torch.Tensor):
+    """Checks the pool layout of muxserve/flexstore/manager.py:456-468, returns (num_blocks, block_size)."""
+    if key_cache.dim() != 4 or value_cache.dim() != 3:
+        raise ValueError("key_cache must be [blocks, D/x, block, x] and value_cache [blocks, D, block]")
+    if not key_cache.is_contiguous() or not value_cache.is_contiguous():
+        raise ValueError("the KV pool tensors must be contiguous")
+    nb, dx, bs, x = key_cache.shape
+    if x * key_cache.element_size() != 16 or dx * x != HEAD_SIZE:
+        raise ValueError(f"key_cache shape {tuple(key_cache.shape)} is not [blocks, {HEAD_SIZE}/x, block, x] with x = 16 bytes")
+    if tuple(value_cache.shape) != (nb, HEAD_SIZE, bs):
+        raise ValueError(f"value_cache shape {tuple(value_cache.shape)} does not match key_cache")
+    if key_cache.dtype != value_cache.dtype:
+        raise TypeError("key_cache and value_cache differ in dtype")
+    return nb, bs
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(nbytes: int, device: torch.device) -> Optional[torch.Tensor]:
+    """Scratch for partitioned (flash-decoding) launches, cached per (device, stream)."""
+    if nbytes == 0:
+        return None
+    key = (device.index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def reshape_and_cache(k: torch.Tensor, v: torch.Tensor, key_cache: torch.Tensor,
+                      value_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Writes the new tokens' K/V rows into their pool slots.
+
+    ``k``, ``v``: [T, H*128] or [T, H, 128] (views of a fused qkv tensor are fine);
+    ``slot_mapping``: int64 [T, H], e.g. ``slot_mapping[:, layer, :]`` of the
+    reference's [T, L, H] tensor (muxserve/flexserver/llm_runtime.py:301-302).
+    Slot ``s`` is offset ``s % block_size`` of block ``s // block_size``
+    (csrc/batch_scheduler.h:58-67); a negative slot skips the row.
+    """
+    _require_cuda(k=k, v=v, key_cache=key_cache, value_cache=value_cache, slot_mapping=slot_mapping)
+    nb, bs = _pool(key_cache, value_cache)
+    T, H, k_ts, k_hs = _rows(k, "k")
+    Tv, Hv, v_ts, v_hs = _rows(v, "v")
+    if (T, H) != (Tv, Hv):
+        raise ValueError("k and v differ in shape")
+    if k.dtype != key_cache.dtype or v.dtype != key_cache.dtype:
+        raise TypeError("k/v dtype differs from the pool dtype")
+    if slot_mapping.dtype != torch.int64:
+        raise TypeError("slot_mapping must be int64")
+    if slot_mapping.dim() == 1 and H == 1:
+        slot_mapping = slot_mapping.unsqueeze(1)
+    if slot_mapping.dim() != 2 or tuple(slot_mapping.shape) != (T, H):
+        raise ValueError(f"slot_mapping must be [tokens, kv_heads] = [{T}, {H}], got {tuple(slot_mapping.shape)}")
+    args = CacheWriteArgs(
+        k=k.data_ptr(), v=v.data_ptr(), k_token_stride=k_ts, k_head_stride=k_hs,
+        v_token_stride=v_ts, v_head_stride=v_hs,
+        key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(), num_blocks=nb,
+        slot_mapping=slot_mapping.data_ptr(),
+        slot_token_stride=slot_mapping.stride(0), slot_head_stride=slot_mapping.stride(1),
+        num_tokens=T, num_kv_heads=H, head_size=HEAD_SIZE, block_size=bs,
+        dtype=_dtype_code(k, "k"), reserved=0)
+    check(lib().mux_reshape_and_cache(C.byref(args), _stream()), "reshape_and_cache")
+
+
+def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
+                    value_cache: torch.Tensor, head_mapping: Optional[torch.Tensor], scale: float,
+                    block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
+                    max_context_len: int, *, num_kv_heads: Optional[int] = None,
+                    partition_size: int = 0, num_stages: int = 0) -> None:
+    """Decode attention of one query token per sequence over the paged pool.
+
+    ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
+    [S, H, max_blocks] — one block list per (sequence, kv head), the per-layer
+    slice of the reference's [L, S, H, max_blocks] tensor
+    (muxserve/flexserver/llm_runtime.py:327) — or [S, max_blocks] when all kv
+    heads share a list.  ``head_mapping``: int32 [Hq] kv head of each q head, or
+    ``None`` for contiguous groups.  ``context_lens``: int32 [S], counting the
+    token written by this step's ``reshape_and_cache``.
+    """
+    _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, head_mapping=head_mapping,
+                  block_tables=block_tables, context_lens=context_lens)
+    nb, bs = _pool(key_cache, value_cache)
+    if bs != block_size:
+        raise ValueError(f"block_size {block_size} does not match the pool's {bs}")
+    S, Hq, q_ss, q_hs = _rows(q, "q")
+    So, Hqo, o_ss, o_hs = _rows(out, "out")
+    if (S, Hq) != (So, Hqo):
+        raise ValueError("q and out differ in shape")
+    if q.dtype != key_cache.dtype or out.dtype != key_cache.dtype:
+        raise TypeError("q/out dtype differs from the pool dtype")
+    if block_tables.dtype != torch.int32 or context_lens.dtype != torch.int32:
+        raise TypeError("block_tables and context_lens must be int32")
+    if context_lens.dim() != 1 or context_lens.shape[0] != S or not context_lens.is_contiguous():
+        raise ValueError("context_lens must be a contiguous [num_seqs] tensor")
+    if block_tables.dim() == 3:
+        if block_tables.stride(2) != 1 and block_tables.shape[2] > 1:
+            raise ValueError("block_tables must be dense along the block dimension")
+        H = block_tables.shape[1]
+        bt_ss, bt_hs = block_tables.stride(0), block_tables.stride(1)
+    elif block_tables.dim() == 2:
+        if block_tables.stride(1) != 1 and block_tables.shape[1] > 1:
+            raise ValueError("block_tables must be dense along the block dimension")
+        H = num_kv_heads if num_kv_heads is not None else Hq
+        bt_ss, bt_hs = block_tables.stride(0), 0
+    else:
+        raise ValueError("block_tables must be [S, H, max_blocks] or [S, max_blocks]")
+    if num_kv_heads is not None and num_kv_heads != H:
+        raise ValueError("num_kv_heads does not match block_tables")
+    if block_tables.shape[0] != S:
+        raise ValueError("block_tables and q differ in the number of sequences")
+    if block_tables.shape[-1] * block_size < max_context_len:
+        raise ValueError("block_tables has fewer blocks per sequence than max_context_len needs")
+    hm_ptr = None
+    if head_mapping is not None:
+        if head_mapping.dtype != torch.int32 or head_mapping.numel() != Hq or not head_mapping.is_contiguous():
+            raise ValueError("head_mapping must be a contiguous int32 [num_q_heads] tensor")
+        hm_ptr = head_mapping.data_ptr()
+    args = AttnArgs(
+        out=out.data_ptr(), q=q.data_ptr(), q_seq_stride=q_ss, q_head_stride=q_hs,
+        out_seq_stride=o_ss, out_head_stride=o_hs,
+        key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(), num_blocks=nb,
+        head_mapping=hm_ptr, block_tables=block_tables.data_ptr(),
+        bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(),
+        scale=float(scale), num_seqs=S, num_q_heads=Hq, num_kv_heads=H, head_size=HEAD_SIZE,
+        block_size=block_size, max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
+        partition_size=partition_size, num_stages=num_stages)
+    L = lib()
+    need = L.mux_paged_attention_workspace_size(C.byref(args))
+    ws = _workspace(need, q.device)
+    check(L.mux_paged_attention(C.byref(args), ws.data_ptr() if ws is not None else None,
+                                ws.numel() if ws is not None else 0, _stream()), "paged_attention")
+
+
+def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
+                          value_cache: torch.Tensor, block_tables: torch.Tensor,
+                          item_context_len: torch.Tensor, item_q_row: torch.Tensor,
+                          item_group: torch.Tensor, item_scale: torch.Tensor, block_size: int,
+                          max_context_len: int, max_group: int, *, partition_size: int = 0,
+                          num_stages: int = 0) -> None:
+    """One launch for the decode batches of several models sharing the pool.
+
+    Item ``i`` is one (sequence, kv head) of some model: q rows
+    ``item_q_row[i] .. + item_group[i]`` of the packed ``q``/``out`` [rows, 128]
+    attend over block list ``block_tables[i]`` with ``item_context_len[i]`` tokens
+    and softmax scale ``item_scale[i]``.  ``muxserve_b200.mixed`` builds these
+    arrays from per-model batches.
+    """
+    _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, block_tables=block_tables,
+                  item_context_len=item_context_len, item_q_row=item_q_row, item_group=item_group,
+                  item_scale=item_scale)
+    nb, bs = _pool(key_cache, value_cache)
+    if bs != block_size:
+        raise ValueError(f"block_size {block_size} does not match the pool's {bs}")
+    if q.dim() != 2 or q.shape[1] != HEAD_SIZE or q.stride(1) != 1 or out.shape != q.shape or out.stride(1) != 1:
+        raise ValueError(f"q and out must be packed [rows, {HEAD_SIZE}] tensors of one shape")
+    if q.dtype != key_cache.dtype or out.dtype != key_cache.dtype:
+        raise TypeError("q/out dtype differs from the pool dtype")
+    n = block_tables.shape[0]
+    if block_tables.dim() != 2 or block_tables.dtype != torch.int32 or (block_tables.shape[1] > 1 and block_tables.stride(1) != 1):
+        raise ValueError("block_tables must be int32 [items, max_blocks], dense along blocks")
+    for name, t, dt in (("item_context_len", item_context_len, torch.int32), ("item_q_row", item_q_row, torch.int32),
+                        ("item_group", item_group, torch.int32), ("item_scale", item_scale, torch.float32)):
+        if t.dtype != dt or t.dim() != 1 or t.shape[0] != n or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous {dt} [items] tensor")
+    if block_tables.shape[1] * block_size < max_context_len:
+        raise ValueError("block_tables has fewer blocks per item than max_context_len needs")
+    args = AttnMixedArgs(
+        out=out.data_ptr(), q=q.data_ptr(), q_row_stride=q.stride(0), out_row_stride=out.stride(0),
+        key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(), num_blocks=nb,
+        block_tables=block_tables.data_ptr(), bt_item_stride=block_tables.stride(0),
+        item_context_len=item_context_len.data_ptr(), item_q_row=item_q_row.data_ptr(),
+        item_group=item_group.data_ptr(), item_scale=item_scale.data_ptr(),
+        num_items=n, max_group=max_group, head_size=HEAD_SIZE, block_size=block_size,
+        max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
+        partition_size=partition_size, num_stages=num_stages)
+    L = lib()
+    need = L.mux_paged_attention_mixed_workspace_size(C.byref(args))
+    ws = _workspace(need, q.device)
+    check(L.mux_paged_attention_mixed(C.byref(args), ws.data_ptr() if ws is not None else None,
+                                      ws.numel() if ws is not None else 0, _stream()),
+          "paged_attention_mixed")
+
+
+def device_status() -> int:
+    """Reads and clears the MUX_DEV_* status bits of the current device (synchronises the stream)."""
+    return check(lib().mux_device_status(_stream()), "device_status")
