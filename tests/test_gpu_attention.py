@@ -1,0 +1,193 @@
+"""paged_attention through the C ABI vs the fp32 gather oracle (tolerance 2e-3 abs + 1e-2 rel)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env(built_lib):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from muxserve_b200 import ops
+    import gpu_util
+    return ops, gu_mod()
+
+
+def gu_mod():
+    import gpu_util
+    return gpu_util
+
+
+def run(ops, gu, case, kc, vc, head_mapping=None, **kw):
+    ops.reshape_and_cache(case.k[0], case.v[0], kc, vc, case.slot_mapping[:, 0, :])
+    out = torch.full_like(case.q[0], float("nan"))
+    ops.paged_attention(out, case.q[0], kc, vc, head_mapping, case.scale, case.block_tables[0],
+                        case.context_lens, case.block_size, case.max_context_len, **kw)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B", [16, 8, 32])
+@pytest.mark.parametrize("group", [1, 8])
+def test_attention_ragged(env, dtype, B, group):
+    ops, gu = env
+    ctx = [1, 2, B - 1, B, B + 1, 255, 256, 257, 300, 511, 77, 1000]
+    H = 3
+    case, kc, vc = gu.make_case(len(ctx), H * group, H, ctx, B, dtype, seed=3 + B + group, num_blocks=2048)
+    out = run(ops, gu, case, kc, vc)
+    kc_c, vc_c, ref = gu.oracle_step(case, kc, vc)
+    assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
+    gu.assert_close(out, ref, f"B={B} G={group} {dtype}")
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("psize,stages", [(16, 4), (64, 4), (128, 8), (512, 8), (1024, 12), (4096, 16)])
+def test_attention_partition_sizes(env, psize, stages):
+    """Every partitioning gives the same answer (single partition up to 63 partitions per sequence)."""
+    ops, gu = env
+    ctx = [1000, 17, 513, 64, 2, 999]
+    case, kc, vc = gu.make_case(len(ctx), 4, 4, ctx, 16, torch.float16, seed=21, num_blocks=1024)
+    out = run(ops, gu, case, kc, vc, partition_size=psize, num_stages=stages)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(out, ref, f"partition {psize}")
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("group", [2, 4, 5, 16, 12])
+def test_attention_group_sizes(env, group):
+    """GQA groups that do not fill, or overflow, one 8-head tile."""
+    ops, gu = env
+    ctx = [300, 31, 129, 16]
+    case, kc, vc = gu.make_case(len(ctx), 2 * group, 2, ctx, 16, torch.bfloat16, seed=group, num_blocks=512)
+    out = run(ops, gu, case, kc, vc)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(out, ref, f"group {group}")
+
+
+def test_attention_head_mapping_interleaved(env):
+    """head_mapping need not be contiguous groups: q head hq reads kv head hq % H."""
+    ops, gu = env
+    ctx = [100, 260, 15]
+    H, G = 4, 3
+    case, kc, vc = gu.make_case(len(ctx), H * G, H, ctx, 16, torch.float16, seed=8, num_blocks=512)
+    hm = (torch.arange(H * G, dtype=torch.int32) % H).cuda()
+    out = run(ops, gu, case, kc, vc, head_mapping=hm)
+    _, _, ref = gu.oracle_step(case, kc, vc, head_mapping=hm)
+    gu.assert_close(out, ref, "interleaved head_mapping")
+    hm2 = (torch.arange(H * G, dtype=torch.int32) // G).cuda()
+    out2 = run(ops, gu, case, kc, vc, head_mapping=hm2)
+    out3 = run(ops, gu, case, kc, vc, head_mapping=None)
+    assert torch.equal(out2, out3)
+    assert ops.device_status() == 0
+
+
+def test_attention_strided_q_and_2d_shapes(env):
+    """q as a view of a fused qkv tensor [S, (Hq+2H)*D]; out 2-D [S, Hq*D]."""
+    ops, gu = env
+    ctx = [33, 200, 90, 7]
+    Hq = H = 5
+    case, kc, vc = gu.make_case(len(ctx), Hq, H, ctx, 16, torch.float16, seed=12, num_blocks=512)
+    S = len(ctx)
+    qkv = torch.zeros(S, 3 * Hq * 128, dtype=torch.float16, device="cuda")
+    qkv[:, :Hq * 128] = case.q[0].reshape(S, -1)
+    q_view = qkv[:, :Hq * 128]
+    ops.reshape_and_cache(case.k[0], case.v[0], kc, vc, case.slot_mapping[:, 0, :])
+    out = torch.empty(S, Hq * 128, dtype=torch.float16, device="cuda")
+    ops.paged_attention(out, q_view, kc, vc, None, case.scale, case.block_tables[0], case.context_lens, 16,
+                        case.max_context_len)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(out.view(S, Hq, 128), ref, "strided q")
+
+
+def test_attention_poisoned_padding_and_stale_tails(env):
+    """Block-table entries past a list's end point at a NaN block and the unwritten tail of every
+    last block is NaN: neither may reach the output (the reference leaves both uninitialised)."""
+    ops, gu = env
+    ctx = [1, 17, 40, 255, 130, 300]
+    case, kc, vc = gu.make_case(len(ctx), 4, 4, ctx, 16, torch.float16, seed=31, num_blocks=1024)
+    used = case.block_tables[case.block_tables >= 0].long()
+    free = torch.ones(1024, dtype=torch.bool, device="cuda")
+    free[used] = False
+    poison = int(torch.nonzero(free)[0])
+    kc[poison], vc[poison] = float("nan"), float("nan")
+    case.block_tables[case.block_tables < 0] = poison
+    for s, c in enumerate(ctx):
+        if c % 16:
+            ids = case.block_tables[0, s, :, (c - 1) // 16].long()
+            kc[ids, :, c % 16:, :] = float("nan")
+            vc[ids, :, c % 16:] = float("nan")
+    out = run(ops, gu, case, kc, vc)
+    assert not torch.isnan(out).any()
+    kc_c, vc_c = torch.nan_to_num(kc.cpu(), nan=0.0), torch.nan_to_num(vc.cpu(), nan=0.0)
+    from oracle.attention_oracle import paged_attention_ref
+    ref = paged_attention_ref(case.q[0].cpu(), kc_c, vc_c, None, case.scale, case.block_tables[0].cpu(),
+                              case.context_lens.cpu(), 16)
+    gu.assert_close(out, ref, "poisoned")
+
+
+def test_attention_known_answers(env):
+    """Properties that hold for any correct implementation, independent of the oracle."""
+    ops, gu = env
+    ctx = [1, 50, 257]
+    case, kc, vc = gu.make_case(len(ctx), 8, 2, ctx, 16, torch.float16, seed=2, num_blocks=256)
+    ops.reshape_and_cache(case.k[0], case.v[0], kc, vc, case.slot_mapping[:, 0, :])
+    out = torch.empty_like(case.q[0])
+    # V == 1 everywhere -> output == 1
+    ops.paged_attention(out, case.q[0], kc, torch.ones_like(vc), None, case.scale, case.block_tables[0],
+                        case.context_lens, 16, case.max_context_len)
+    assert torch.allclose(out.float(), torch.ones_like(out).float(), atol=1e-3)
+    # a one-token context returns that token's V row
+    ops.paged_attention(out, case.q[0], kc, vc, None, case.scale, case.block_tables[0], case.context_lens, 16,
+                        case.max_context_len)
+    v_new = case.v[0].view(3, 2, 128)[0]                       # seq 0, both kv heads
+    assert torch.equal(out[0].view(2, 4, 128), v_new.unsqueeze(1).expand(2, 4, 128))
+    # q == 0 -> uniform weights -> mean of V over the context
+    ops.paged_attention(out, torch.zeros_like(case.q[0]), kc, vc, None, case.scale, case.block_tables[0],
+                        case.context_lens, 16, case.max_context_len)
+    from oracle.attention_oracle import gather_kv
+    _, v = gather_kv(kc.cpu(), vc.cpu(), case.block_tables[0, 2, 1, :17].cpu(), 257)
+    assert torch.allclose(out[2, 4].float().cpu(), v.mean(0), atol=2e-3, rtol=1e-2)
+
+
+def test_attention_edge_cases(env):
+    ops, gu = env
+    from muxserve_b200 import _lib
+    kc = torch.randn(64, 16, 16, 8, device="cuda").half()
+    vc = torch.randn(64, 128, 16, device="cuda").half()
+    # empty batch
+    e = torch.empty(0, 4, 128, dtype=torch.float16, device="cuda")
+    ops.paged_attention(e, e, kc, vc, None, 0.1, torch.empty(0, 4, 1, dtype=torch.int32, device="cuda"),
+                        torch.empty(0, dtype=torch.int32, device="cuda"), 16, 0)
+    # a zero-length context yields zeros and touches no block
+    q = torch.randn(2, 4, 128, device="cuda").half()
+    out = torch.full_like(q, float("nan"))
+    bt = torch.zeros(2, 4, 2, dtype=torch.int32, device="cuda")
+    ops.paged_attention(out, q, kc, vc, None, 0.1, bt, torch.tensor([0, 20], dtype=torch.int32, device="cuda"), 16, 20)
+    assert float(out[0].abs().sum()) == 0.0 and not torch.isnan(out[1]).any()
+    assert ops.device_status() == 0
+    # out-of-range block ids and over-long contexts are reported, not dereferenced
+    bt[1, 2, 0] = 64
+    ops.paged_attention(out, q, kc, vc, None, 0.1, bt, torch.tensor([5, 20], dtype=torch.int32, device="cuda"), 16, 20)
+    assert ops.device_status() == _lib.MUX_DEV_BAD_BLOCK_ID
+    bt[1, 2, 0] = 0
+    ops.paged_attention(out, q, kc, vc, None, 0.1, bt, torch.tensor([5, 33], dtype=torch.int32, device="cuda"), 16, 32)
+    assert ops.device_status() == _lib.MUX_DEV_BAD_CONTEXT
+    with pytest.raises(ValueError):
+        ops.paged_attention(out, q, kc, vc, None, 0.1, bt, torch.tensor([5, 20], dtype=torch.int32, device="cuda"), 16, 64)
+    with pytest.raises(ValueError):
+        ops.paged_attention(out, q, kc, vc, None, 0.1, bt, torch.tensor([5, 20], dtype=torch.int32, device="cuda"), 8, 20)
+
+
+def test_attention_max_context_8192_gqa(env):
+    """Longest configured context (8192 + 8 new tokens) with the GQA group of 8."""
+    ops, gu = env
+    ctx = [8200, 2048, 5000]
+    case, kc, vc = gu.make_case(len(ctx), 8, 1, ctx, 16, torch.bfloat16, seed=4, num_blocks=2048, new_tokens=8)
+    ops.reshape_and_cache(case.k[0], case.v[0], kc, vc, case.slot_mapping[:, 0, :])
+    out = torch.empty_like(case.q[0])
+    for psize in (0, 512, 2048):
+        ops.paged_attention(out, case.q[0], kc, vc, None, case.scale, case.block_tables[0], case.context_lens, 16,
+                            case.max_context_len, partition_size=psize)
+        _, _, ref = gu.oracle_step(case, kc, vc)
+        gu.assert_close(out, ref, f"ctx 8200 partition {psize}")
