@@ -1,0 +1,444 @@
+#!/usr/bin/env python
+"""Benchmark of the decode attention path (reshape_and_cache + paged_attention over all layers).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c5] [--impl native|reference]
+
+A step is one decode step of the path: for every layer one cache write of the new
+tokens and one paged attention over the sequence batch.  Prints ONE JSON line.
+``--impl reference`` times the CPU oracle (the reference has no CPU implementation
+of these ops; its kernels live in an un-vendored fork) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = ("paged decode-attn tokens/s (reshape_and_cache + paged_attention over all layers; "
+          "achieved HBM GB/s and fraction of peak in `roofline`)")
+
+# name -> global (un-sharded) shape.  Workload text follows the benchmark configurations.
+WORKLOADS = {
+    "c2": dict(desc="LLaMA-7B shape fp16 decode: 32 layers, 32 heads (MHA), head_dim 128, batch 64, "
+                    "context_lens U[128,2048], block_size 16, 1 new token/seq",
+               L=32, Hq=32, H=32, S=64, lo=128, hi=2048, dtype="f16", new_tokens=1),
+    "c4": dict(desc="LLaMA-65B shape bf16 decode: 80 layers, 64 heads (MHA), batch 128, context_lens U[512,4096], "
+                    "block_size 16",
+               L=80, Hq=64, H=64, S=128, lo=512, hi=4096, dtype="bf16", new_tokens=1),
+    "c5": dict(desc="Llama-2-70B shape bf16 GQA decode: 80 layers, 64 q heads / 8 kv heads, batch 256, "
+                    "context_lens U[2048,8192], block_size 16, 8 new tokens/seq",
+               L=80, Hq=64, H=8, S=256, lo=2048, hi=8192, dtype="bf16", new_tokens=8),
+}
+BLOCK = 16
+DTYPES = {"f16": torch.float16, "bf16": torch.bfloat16}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
+    ap.add_argument("--pool-frac", type=float, default=0.6, help="fraction of HBM given to the KV pool")
+    ap.add_argument("--partition-size", type=int, default=0)
+    ap.add_argument("--num-stages", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiler captures)")
+    ap.add_argument("--seed", type=int, default=20240531)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel leg at N > 1")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
+    return ap.parse_args()
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback 6650 GB/s (MEASURED_PEAKS.json absent)"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (read-only NVML)."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def __init__(self, device_index: int, period_s: float = 0.01):
+        super().__init__(daemon=True)
+        self.period = period_s
+        self.samples, self.reason_bits, self.sm_max = [], 0, None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception as exc:  # NVML missing: fall back to one nvidia-smi query per sample
+            self.err = repr(exc)
+            self.dev = device_index
+
+    def _sample(self):
+        if self.ok:
+            nv = self.nv
+            mhz = int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            try:
+                bits = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception:
+                bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+            return mhz, bits
+        out = subprocess.run(["nvidia-smi", "-i", str(self.dev), "--query-gpu=clocks.sm,clocks.max.sm,"
+                              "clocks_event_reasons.active", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip().split(",")
+        self.sm_max = int(out[1])
+        return int(out[0]), int(out[2], 16)
+
+    def run(self):
+        while not self._stop_evt.is_set():
+            try:
+                mhz, bits = self._sample()
+                self.samples.append(mhz)
+                self.reason_bits |= bits
+            except Exception:
+                pass
+            self._stop_evt.wait(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=5)
+        s = sorted(self.samples)
+        reasons = [name for bit, name in self.REASONS.items() if self.reason_bits & bit]
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.sm_max, "reasons": reasons,
+                "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------- CPU oracle legs
+def compact_layer_to_cpu(case, kc, vc, layer):
+    """Copies the blocks one layer touches into a small CPU pool with renumbered ids."""
+    bt = case.block_tables[layer]
+    valid = bt >= 0
+    ids = bt[valid].long()
+    remap = torch.zeros_like(bt)
+    remap[valid] = torch.arange(ids.numel(), dtype=torch.int32, device=bt.device)
+    return kc[ids].cpu(), vc[ids].cpu(), remap.cpu()
+
+
+def cpu_attention_step(q, k_new, v_new, kc, vc, bt, slots, ctx, scale, seqs):
+    """One layer of the path on the CPU oracle for the first `seqs` sequences."""
+    from oracle.attention_oracle import paged_attention_ref_batched
+    from oracle.cache_write_oracle import reshape_and_cache_ref
+    T_per = k_new.shape[0] // q.shape[0]
+    reshape_and_cache_ref(k_new[:seqs * T_per], v_new[:seqs * T_per], kc, vc, slots[:seqs * T_per])
+    return paged_attention_ref_batched(q[:seqs], kc, vc, scale, bt[:seqs], ctx[:seqs], BLOCK)
+
+
+def time_cpu_sample(q, k_new, v_new, kc, vc, bt, slots, ctx, scale, budget_s, reps_max=6):
+    """Times the oracle on all sequences of one layer, repeating until about `budget_s` seconds are spent."""
+    S = q.shape[0]
+    times = []
+    t_all = time.perf_counter()
+    while len(times) < reps_max and (not times or time.perf_counter() - t_all < budget_s):
+        t0 = time.perf_counter()
+        cpu_attention_step(q, k_new, v_new, kc, vc, bt, slots, ctx, scale, S)
+        times.append(time.perf_counter() - t0)
+    return min(times), len(times)
+
+
+def synth_cpu_layer(w, seed, seqs=None):
+    """A compact CPU-only layer of workload `w` (no GPU involved): pool = exactly the blocks it needs, shuffled."""
+    from muxserve_b200 import workloads
+    gen = torch.Generator().manual_seed(seed)
+    S = w["S"] if seqs is None else min(seqs, w["S"])
+    ctx = workloads.uniform_context_lens(w["S"], w["lo"], w["hi"], gen)[:S]
+    nblk = workloads.blocks_needed(ctx, 1, w["H"], BLOCK)
+    perm = torch.randperm(nblk, generator=gen)
+    bt, _ = workloads.scatter_block_tables(ctx, 1, w["H"], BLOCK, perm)
+    slots = workloads.last_token_slots(bt, ctx, BLOCK, w["new_tokens"])[:, 0, :]
+    dt = DTYPES[w["dtype"]]
+    kc = torch.randn((nblk, 16, BLOCK, 8), generator=gen).to(dt)
+    vc = torch.randn((nblk, 128, BLOCK), generator=gen).to(dt)
+    q = torch.randn((S, w["Hq"], 128), generator=gen).to(dt)
+    k = torch.randn((S * w["new_tokens"], w["H"], 128), generator=gen).to(dt)
+    v = torch.randn((S * w["new_tokens"], w["H"], 128), generator=gen).to(dt)
+    return q, k, v, kc, vc, bt[0].clamp_min(0), slots, ctx
+
+
+def run_reference(args):
+    """CPU arm: the oracle on all host threads; a step is one layer of the workload over a bounded
+    number of sequences, scaled to the full layer count."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    # calibrate on 2 sequences, then size the per-step sample so that the whole run stays near 2 minutes
+    q, k, v, kc, vc, bt, slots, ctx = synth_cpu_layer(w, args.seed, seqs=2)
+    t0 = time.perf_counter()
+    cpu_attention_step(q, k, v, kc, vc, bt, slots, ctx, 128 ** -0.5, 2)
+    t_seq = (time.perf_counter() - t0) / 2
+    budget = 120.0
+    seqs = int(max(1, min(w["S"], budget / max(1e-6, (args.steps + args.warmup) * t_seq))))
+    q, k, v, kc, vc, bt, slots, ctx = synth_cpu_layer(w, args.seed, seqs=seqs)
+    for _ in range(args.warmup):
+        cpu_attention_step(q, k, v, kc, vc, bt, slots, ctx, 128 ** -0.5, seqs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_attention_step(q, k, v, kc, vc, bt, slots, ctx, 128 ** -0.5, seqs)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    tokens_per_s = seqs / (dt * w["L"])            # one layer timed; a decode step runs L of them
+    sample = (f"each step = 1 of {w['L']} layers over {seqs} of {w['S']} sequences on the CPU oracle "
+              f"(fp32 PyTorch gather attention + scatter cache write); tokens/s = sequences / (step time x {w['L']} layers)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tokens_per_s, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * w["L"] * (w["S"] / seqs),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['desc']}", "block_size": BLOCK, "seed": args.seed},
+        "cpu_baseline": {"value": tokens_per_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tokens_per_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference ships no CPU (or CUDA) source for these ops; this arm is the oracle port",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- native arm
+def run_native(args):
+    import torch.distributed as dist
+    from muxserve_b200 import flexstore, ops, workloads
+    from muxserve_b200.host_step import HostDecodeStep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl native needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = dict(WORKLOADS[args.workload])
+    if args.layers > 0:
+        w["L"] = args.layers
+    dt = DTYPES[w["dtype"]]
+    L, S, Hq, H, NT = w["L"], w["S"], w["Hq"], w["H"], w["new_tokens"]
+
+    # ---- pool sized as FlexStore does, a fraction of HBM ----
+    total_mem = torch.cuda.get_device_properties(dev).total_memory
+    num_blocks = flexstore.get_num_gpu_blocks(total_mem, args.pool_frac, BLOCK)
+    kc, vc = flexstore.allocate_gpu_cache(num_blocks, BLOCK, dt, dev)
+    workloads.fill_pool_(kc, vc, args.seed + 17 * rank)
+
+    gen = torch.Generator().manual_seed(args.seed + 1000 * rank)
+    ctx = workloads.uniform_context_lens(S, w["lo"], w["hi"], gen)
+    per_layer = workloads.blocks_needed(ctx, 1, H, BLOCK)
+    L_res = max(1, min(L, int(num_blocks * 0.98) // per_layer))     # distinct resident layers
+    shape = workloads.ModelShape(args.workload, L_res, Hq, H, S)
+    case = workloads.make_decode_case(shape, ctx, block_size=BLOCK, num_blocks=num_blocks, dtype=dt, device=dev,
+                                      seed=args.seed + 1000 * rank, new_tokens=NT)
+    ctx_list = ctx.tolist()
+    attn_bytes = workloads.attention_bytes(ctx_list, Hq, H, BLOCK)
+    cw_bytes = workloads.cache_write_bytes(S * NT, H)
+    out = torch.empty((S, Hq, 128), dtype=dt, device=dev)
+    psize, nst = args.partition_size, args.num_stages
+
+    def layer(l, ev=None):
+        r = l % L_res
+        ops.reshape_and_cache(case.k[r], case.v[r], kc, vc, case.slot_mapping[:, r, :])
+        if ev is not None:
+            ev[0].record()
+        ops.paged_attention(out, case.q[r], kc, vc, None, case.scale, case.block_tables[r], case.context_lens,
+                            BLOCK, case.max_context_len, partition_size=psize, num_stages=nst)
+        if ev is not None:
+            ev[1].record()
+
+    def step(events=None):
+        for l in range(L):
+            layer(l, None if events is None else events[l])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident leg ----
+    for _ in range(max(3, args.warmup)):
+        step()
+    status_warm = ops.device_status()
+    events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L)]
+              for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = ops.launch_count
+    e0.record()
+    for i in range(args.steps):
+        step(events[i])
+    e1.record()
+    gpu_launches = ops.launch_count - launches0
+    barrier()
+    clocks = sampler.stop()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    attn_ms = sum(a.elapsed_time(b) for evs in events for a, b in evs) / (args.steps * L)
+    status = ops.device_status() | status_warm
+
+    # ---- end-to-end leg: host buffers, copies inside the timed region ----
+    e2e = None
+    if not args.no_e2e:
+        hs = HostDecodeStep(workloads.ModelShape(args.workload, L, Hq, H, S), BLOCK, dt, kc, vc,
+                            case.block_tables.shape[-1], new_tokens=NT, partition_size=psize, num_stages=nst)
+        rep = [l % L_res for l in range(L)]
+        pin = lambda t: t.cpu().pin_memory()
+        qh, kh, vh = pin(case.q[rep]), pin(case.k[rep]), pin(case.v[rep])
+        bth = pin(case.block_tables[rep].clamp_min(0))
+        smh = pin(case.slot_mapping[:, rep, :].contiguous())
+        ch = pin(case.context_lens)
+        oh = torch.empty((L, S, Hq, 128), dtype=dt).pin_memory()
+        for _ in range(3):
+            hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len)
+        e1.record()
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+        e2e = {"value": world * S / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": hs.h2d_bytes, "d2h_bytes_per_step": hs.d2h_bytes,
+               "how": "HostDecodeStep.run: pinned host q/k/v/block_tables/slot_mapping/context_lens -> device, "
+                      "ops, out -> pinned host, per layer on copy streams overlapped with the kernels"}
+        status |= ops.device_status()
+        del qh, kh, vh, bth, smh, oh
+
+    # ---- tensor-parallel leg (N > 1): the same model sharded by kv head + NCCL all-reduce of the output ----
+    tp = None
+    if world > 1 and not args.no_tp and H % world == 0:
+        Hl, Hql = H // world, Hq // world
+        full = torch.zeros((S, Hq * 128), dtype=dt, device=dev)
+
+        def tp_step(allreduce=True, attention=True):
+            for l in range(L):
+                r = l % L_res
+                if attention:
+                    ops.reshape_and_cache(case.k[r][:, :Hl], case.v[r][:, :Hl], kc, vc, case.slot_mapping[:, r, :Hl])
+                    ops.paged_attention(out[:, :Hql], case.q[r][:, :Hql], kc, vc, None, case.scale,
+                                        case.block_tables[r][:, :Hl], case.context_lens, BLOCK, case.max_context_len,
+                                        partition_size=psize, num_stages=nst)
+                if allreduce:
+                    dist.all_reduce(full)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            barrier()
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            barrier()
+            return max_over_ranks(e0.elapsed_time(e1)) / args.steps
+
+        ms_tp = timed(tp_step)
+        ms_ar = timed(lambda: tp_step(attention=False))
+        ms_at = timed(lambda: tp_step(allreduce=False))
+        tp = {"tp": world, "scaling": "strong", "tokens_per_s": S / (ms_tp * 1e-3), "ms_per_step": ms_tp,
+              "attention_only_ms_per_step": ms_at, "allreduce_only_ms_per_step": ms_ar,
+              "allreduce_bytes": full.numel() * full.element_size(),
+              "note": "kv heads sharded over ranks (no cross-GPU traffic in attention); one NCCL all-reduce of the "
+                      "[batch, hidden] output per layer"}
+
+    # ---- CPU baseline on a bounded sample (rank 0, N = 1 only) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        kcc, vcc, btc = compact_layer_to_cpu(case, kc, vc, 0)
+        # slots of layer 0 renumbered into the compact pool
+        slots = workloads.last_token_slots(btc.unsqueeze(0), ctx, BLOCK, NT)[:, 0, :]
+        t_layer, reps = time_cpu_sample(case.q[0].cpu(), case.k[0].cpu(), case.v[0].cpu(), kcc, vcc, btc, slots,
+                                        ctx, case.scale, args.cpu_seconds)
+        cpu = {"value": S / (t_layer * L), "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"layer 0 of {L} (all {S} sequences, its own KV blocks copied to a compact host pool), "
+                         f"best of {reps} runs of {t_layer:.2f} s on the CPU oracle, scaled x{L} layers"}
+
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+        path_gbs = (attn_bytes + cw_bytes) * L / (ms_step * 1e-3) / 1e9
+        traffic = None
+        tf = ROOT / "profiles" / "traffic.json"
+        if tf.exists():
+            try:
+                traffic = json.loads(tf.read_text()).get(args.workload, {}).get("dram_bytes_per_launch")
+            except Exception:
+                traffic = None
+        line = {
+            "metric": METRIC, "value": world * S / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['desc']}", "block_size": BLOCK, "seed": args.seed,
+                       "pool": f"{num_blocks} blocks = {num_blocks * 8192 / 1e9:.1f} GB ({args.pool_frac:.0%} of HBM), "
+                               "block lists scattered without replacement over the whole pool",
+                       "resident_layers": L_res, "layers": L,
+                       "l2": f"no flush: one step streams {attn_bytes * min(L, L_res) / 1e9:.1f} GB of distinct KV "
+                             "blocks, far above the 126 MB L2",
+                       "placement": ("1 model on 1 GPU" if world == 1 else
+                                     f"{world} independent model replicas, one per GPU, no data-path collective"),
+                       "partition_size": psize or "library default", "num_stages": nst or "library default"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "kernel": "paged_attn_kernel (+ merge kernel when partitioned)",
+                         "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": attn_ms, "peak_source": peak_src,
+                         "whole_path_gbs": path_gbs},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
+            "clocks": clocks, "device_status": status,
+        }
+        if tp is not None:
+            line["tp"] = tp
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

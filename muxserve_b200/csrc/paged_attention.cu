@@ -12,7 +12,8 @@
 // bytes are used as they arrive.
 //
 //   phase 1  logits[h][t] = scale * K[t,:] . q[h,:]   for all K blocks of the unit
-//   softmax  over the unit (max, exp, sum) -> P in the KV dtype
+//   softmax  over the unit (max, exp, sum) -> P split into hi + lo parts of the KV dtype
+//            (two MMAs per tile; keeps fp32-level accuracy of P with 16-bit operands)
 //   phase 2  out^T[d][h] += V^T[d,t] P^T[t,h]         for all V blocks of the unit
 //
 // A unit that covers its whole context writes `out`; otherwise it writes an
@@ -84,7 +85,7 @@ __host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs
   off += (s_bytes > red_bytes ? s_bytes : red_bytes);
   off = (off + 15) & ~15;
   L.pm = off;
-  off += gs * L.prow * 2;
+  off += 2 * gs * L.prow * 2;  // P as hi + lo planes
   off = (off + 15) & ~15;
   L.ids = off;
   off += pb * 4;
@@ -317,10 +318,13 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     m = warp_max(m);
     float l = 0.f;
     T* prow = Pm + n * PROW;
+    T* prow_lo = prow + p.gs * PROW;
     for (int t = lane; t < nblk * BS; t += 32) {
       float pv = t < ntok ? __expf(srow[t] - m) : 0.f;
       l += pv;
-      prow[t] = from_float<T>(pv);
+      const T hi = from_float<T>(pv);
+      prow[t] = hi;
+      prow_lo[t] = from_float<T>(pv - to_float(hi));
     }
     l = warp_sum(l);
     if (lane == 0) {
@@ -348,11 +352,15 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
         // This lane's four tokens of the k-step: slots {2tq,2tq+1} and {8+2tq,9+2tq}
         // of the MMA are tokens t0..t0+3 (same mapping in A and B).
         const int t0 = ks * 16 + 4 * tq;
-        uint32_t b0 = 0u, b1 = 0u;
+        uint32_t b0 = 0u, b1 = 0u, c0 = 0u, c1 = 0u;
         if (g < geff && lane_has) {
-          uint2 pv = lds64(pm_base + (g * PROW + jb * BS + t0) * 2);
+          const uint32_t pa = pm_base + (g * PROW + jb * BS + t0) * 2;
+          uint2 pv = lds64(pa);
           b0 = pv.x;
           b1 = pv.y;
+          pv = lds64(pa + p.gs * PROW * 2);
+          c0 = pv.x;
+          c1 = pv.y;
         }
         uint32_t mlo = 0xffffffffu, mhi = 0xffffffffu;
         if (rem < BS) {  // stale tail of the last block may hold anything, NaN included
@@ -367,6 +375,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
           uint2 r1 = lds64(tile + (row + 8) * VROW + t0 * 2);
           uint32_t a[4] = {r0.x & mlo, r1.x & mlo, r0.y & mhi, r1.y & mhi};
           mma_16816<T>(acc[mt], a, b0, b1);
+          mma_16816<T>(acc[mt], a, c0, c1);
         }
       }
       __syncwarp();
@@ -461,7 +470,7 @@ static int default_stages(int block_size) {
 static Plan make_plan(long long items, int group, int block_size, int max_context_len,
                       int partition_size, int num_stages) {
   Plan pl;
-  int psize = partition_size > 0 ? partition_size : 256;
+  int psize = partition_size > 0 ? partition_size : 512;
   psize = std::max(block_size, (psize / block_size) * block_size);
   pl.pb = psize / block_size;
   pl.max_parts = std::max(1, (max_context_len + psize - 1) / psize);

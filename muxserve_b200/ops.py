@@ -21,6 +21,7 @@ HEAD_SIZE = 128
 
 _DTYPES = {torch.float16: _lib.MUX_DTYPE_F16, torch.bfloat16: _lib.MUX_DTYPE_BF16}
 _workspaces = {}
+launch_count = 0  # kernels enqueued by this module so far (cache write 1; attention 1, or 2 when partitioned)
 
 
 def _dtype_code(t: torch.Tensor, name: str) -> int:
@@ -121,6 +122,8 @@ def reshape_and_cache(k: torch.Tensor, v: torch.Tensor, key_cache: torch.Tensor,
         num_tokens=T, num_kv_heads=H, head_size=HEAD_SIZE, block_size=bs,
         dtype=_dtype_code(k, "k"), reserved=0)
     check(lib().mux_reshape_and_cache(C.byref(args), _stream()), "reshape_and_cache")
+    global launch_count
+    launch_count += 1 if T > 0 else 0
 
 
 def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
@@ -190,6 +193,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
     ws = _workspace(need, q.device)
     check(L.mux_paged_attention(C.byref(args), ws.data_ptr() if ws is not None else None,
                                 ws.numel() if ws is not None else 0, _stream()), "paged_attention")
+    global launch_count
+    launch_count += 0 if S == 0 else (2 if need > 0 else 1)
 
 
 def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
@@ -240,6 +245,8 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
     check(L.mux_paged_attention_mixed(C.byref(args), ws.data_ptr() if ws is not None else None,
                                       ws.numel() if ws is not None else 0, _stream()),
           "paged_attention_mixed")
+    global launch_count
+    launch_count += 0 if n == 0 else (2 if need > 0 else 1)
 
 
 def device_status() -> int:

@@ -65,6 +65,20 @@ def test_attention_group_sizes(env, group):
     gu.assert_close(out, ref, f"group {group}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_attention_short_contexts_cancellation(env, dtype):
+    """Few-token contexts: the output is a signed mix of two or three V rows and is often near zero,
+    so any loss of precision in the softmax weights shows against the absolute tolerance."""
+    ops, gu = env
+    gen = torch.Generator().manual_seed(99)
+    ctx = torch.randint(1, 7, (96,), generator=gen).tolist()
+    case, kc, vc = gu.make_case(len(ctx), 8, 4, ctx, 16, dtype, seed=40, num_blocks=1024)
+    vc.mul_(4.0)                                  # larger values, larger cancellation
+    out = run(ops, gu, case, kc, vc)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(out, ref, f"short contexts {dtype}")
+
+
 def test_attention_head_mapping_interleaved(env):
     """head_mapping need not be contiguous groups: q head hq reads kv head hq % H."""
     ops, gu = env
