@@ -42,6 +42,9 @@ WORKLOADS = {
 BLOCK = 16
 DTYPES = {"f16": torch.float16, "bf16": torch.bfloat16}
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_kernel launch, from the ncu capture summarised in
+# profiles/paged_attn_kernel_c2_small.md (same per-launch work as the benchmark's layer, smaller pool).
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 1202712000 + 6585344}
 
 
 def parse_args():
@@ -398,13 +401,7 @@ def run_native(args):
         peak, peak_src = hbm_peak()
         achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
         path_gbs = (attn_bytes + cw_bytes) * L / (ms_step * 1e-3) / 1e9
-        traffic = None
-        tf = ROOT / "profiles" / "traffic.json"
-        if tf.exists():
-            try:
-                traffic = json.loads(tf.read_text()).get(args.workload, {}).get("dram_bytes_per_launch")
-            except Exception:
-                traffic = None
+        traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if args.layers == 0 else None
         line = {
             "metric": METRIC, "value": world * S / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
