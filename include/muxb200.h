@@ -139,6 +139,24 @@ size_t mux_paged_attention_workspace_size(const mux_attn_args_t* args);
 int mux_paged_attention(const mux_attn_args_t* args, void* workspace,
                         size_t workspace_bytes, void* cuda_stream);
 
+/* No counterpart in the reference.  Same operation and arguments as
+ * mux_paged_attention, for callers that cannot allocate device memory while
+ * they run (a worker whose footprint was fixed at start-up, a process sharing
+ * the GPU that must not grow, a path on which cudaMalloc is not permitted):
+ * the flash-decoding scratch is a fixed MUX_STATIC_SCRATCH_BYTES array inside
+ * the library image, so the call itself never allocates or frees anything.
+ *  - Returns MUX_ERR_TOO_LARGE when mux_paged_attention_workspace_size(args)
+ *    exceeds MUX_STATIC_SCRATCH_BYTES; fall back to mux_paged_attention then.
+ *  - The first call on each device resolves the array's device address; make
+ *    that first call outside of any stream capture.
+ *  - All calls on a device share the one array: two calls whose kernels can
+ *    overlap on the GPU (different streams, no ordering) race on it.  Calls on
+ *    one stream, or otherwise ordered, are safe; stale contents are harmless
+ *    because every value read is written earlier in the same call.
+ *  - Every GPU that loads the library holds the array until process exit. */
+#define MUX_STATIC_SCRATCH_BYTES (16u << 20)
+int mux_paged_attention_static_scratch(const mux_attn_args_t* args, void* cuda_stream);
+
 /* ------------------------------------------------------------------------
  * paged_attention, mixed-model form — ONE launch serves the decode batches
  * of several colocated models that share the pool.  No counterpart in the

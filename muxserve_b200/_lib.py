@@ -82,6 +82,7 @@ SIGNATURES = {
     "mux_reshape_and_cache": (C.c_int, [C.POINTER(CacheWriteArgs), C.c_void_p]),
     "mux_paged_attention_workspace_size": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "mux_paged_attention": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mux_paged_attention_static_scratch": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "mux_paged_attention_mixed_workspace_size": (C.c_size_t, [C.POINTER(AttnMixedArgs)]),
     "mux_paged_attention_mixed": (C.c_int, [C.POINTER(AttnMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),

@@ -21,6 +21,7 @@
 // small kernel merges the partitions (flash-decoding).
 #include <algorithm>
 #include <cstdint>
+#include <mutex>
 
 #include "internal.h"
 #include "ptx.cuh"
@@ -692,3 +693,56 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of mux_paged_attention.
+//
+// Some hosts of this library may not call cudaMalloc once they are running: a
+// serving worker whose memory budget was fixed at start-up (FlexStore gives the
+// KV pool a set fraction of HBM and the rest is spoken for), a process that
+// shares the GPU with others under MPS and must not grow, or code on a path
+// where allocation calls are simply not allowed.  For them the split-K scratch
+// lives in a fixed array inside the library image instead of a caller buffer.
+// Every GPU that loads the library carries the array until the process exits.
+namespace mux {
+
+constexpr size_t kStaticScratchBytes = MUX_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime's symbol
+// table, not something a kernel can dereference; the real device address is
+// looked up once per device (with that device current) and remembered.
+static void* g_static_scratch_addr[kMaxDevicesTracked] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (dev < 0 || dev >= kMaxDevicesTracked) return record_cuda_error(cudaErrorInvalidDevice);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return MUX_OK;
+}
+
+}  // namespace mux
+
+extern "C" int mux_paged_attention_static_scratch(const mux_attn_args_t* a, void* cuda_stream) {
+  int st = mux::validate(a);
+  if (st != MUX_OK) return st;
+  if (a->num_seqs == 0) return MUX_OK;
+  const size_t need = mux_paged_attention_workspace_size(a);
+  if (need > mux::kStaticScratchBytes) return MUX_ERR_TOO_LARGE;  // use mux_paged_attention with your own buffer
+  void* scratch = nullptr;
+  st = mux::static_scratch_address(&scratch);
+  if (st != MUX_OK) return st;
+  // Nothing in the scratch has to start at zero: every partial that the merge
+  // kernel reads is written by the attention kernel of the same call first.
+  return mux_paged_attention(a, scratch, mux::kStaticScratchBytes, cuda_stream);
+}
