@@ -39,6 +39,12 @@ WORKLOADS = {
                     "context_lens U[2048,8192], block_size 16, 8 new tokens/seq",
                L=80, Hq=64, H=8, S=256, lo=2048, hi=8192, dtype="bf16", new_tokens=8),
 }
+# config 3: three colocated LLaMA models sharing one pool on 4 GPUs (TP=4 -> local heads 8/10/13), batches 48/24/12
+C3_MODELS = [("llama-7b", 32, 32, 48), ("llama-13b", 40, 40, 24), ("llama-30b", 60, 52, 12)]   # name, layers, heads, batch
+C3_TP = 4
+C3_DESC = ("three colocated LLaMA models (7B/13B/30B: 32/40/52 heads, 32/40/60 layers, head_dim 128, fp16) sharing one "
+           "head-granular pool, TP=4 share of one GPU (local heads 8/10/13), batches 48/24/12, context_lens lognormal "
+           "(median 256, sigma 1.0) clipped to [16,4096], block lists interleaved randomly, one fused launch per layer")
 BLOCK = 16
 DTYPES = {"f16": torch.float16, "bf16": torch.bfloat16}
 FALLBACK_HBM_GBS = 6650.0
@@ -53,7 +59,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="c2")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["c3"], default="c2")
     ap.add_argument("--pool-frac", type=float, default=0.6, help="fraction of HBM given to the KV pool")
     ap.add_argument("--partition-size", type=int, default=0)
     ap.add_argument("--num-stages", type=int, default=0)
@@ -429,10 +435,124 @@ def run_native(args):
         dist.destroy_process_group()
 
 
+def run_native_c3(args):
+    """Config 3: the per-GPU share of three colocated models, one fused attention launch per layer index
+    (layers 0-31 serve all three models, 32-39 two, 40-59 one) plus one cache write per model and layer."""
+    import torch.distributed as dist
+    from muxserve_b200 import flexstore, mixed, ops, workloads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dt = torch.float16
+    total_mem = torch.cuda.get_device_properties(dev).total_memory
+    num_blocks = flexstore.get_num_gpu_blocks(total_mem, args.pool_frac, BLOCK)
+    kc, vc = flexstore.allocate_gpu_cache(num_blocks, BLOCK, dt, dev)
+    workloads.fill_pool_(kc, vc, args.seed)
+    gen = torch.Generator().manual_seed(args.seed)               # same batch on every rank (TP shares sequences)
+    perm = torch.randperm(num_blocks, generator=gen).to(dev)
+    batches, cases, nxt = [], [], 0
+    for name, L, heads, S in C3_MODELS:
+        Hl = heads // C3_TP
+        ctx = workloads.lognormal_context_lens(S, 256.0, 1.0, 16, 4096, gen)
+        case = workloads.make_decode_case(workloads.ModelShape(name, L, Hl, Hl, S), ctx, block_size=BLOCK,
+                                          num_blocks=num_blocks, dtype=dt, device=dev, seed=args.seed + len(cases),
+                                          block_ids=perm, first_block=nxt, input_layers=4)
+        nxt = case.extra["next_block"]
+        cases.append(case)
+        batches.append(mixed.ModelBatch(name, L, Hl, Hl, 128 ** -0.5, ctx, case.block_tables))
+    plan = mixed.build_mixed_plan(batches, dev)
+    L_max = max(plan.layers)
+    packed_q = [mixed.pack_rows(plan, [c.q[i % c.q.shape[0]] for c in cases]) for i in range(4)]
+    out = torch.empty_like(packed_q[0])
+    psize, nst = args.partition_size, args.num_stages
+    attn_bytes, cw_bytes = [], []
+    for l in range(L_max):
+        a = w = 0
+        for b in batches:
+            if b.num_layers > l:
+                a += workloads.attention_bytes(b.context_lens.tolist(), b.num_q_heads, b.num_kv_heads, BLOCK)
+                w += workloads.cache_write_bytes(b.num_seqs, b.num_kv_heads)
+        attn_bytes.append(a)
+        cw_bytes.append(w)
+
+    def step(events=None):
+        for l in range(L_max):
+            for c in cases:
+                if c.shape.num_layers > l:
+                    r = l % c.k.shape[0]
+                    ops.reshape_and_cache(c.k[r], c.v[r], kc, vc, c.slot_mapping[:, l, :])
+            n_items, n_rows = plan.active(l)
+            if events is not None:
+                events[l][0].record()
+            ops.paged_attention_mixed(out[:n_rows], packed_q[l % 4][:n_rows], kc, vc, plan.block_tables[l, :n_items],
+                                      plan.item_context_len[:n_items], plan.item_q_row[:n_items],
+                                      plan.item_group[:n_items], plan.item_scale[:n_items], BLOCK,
+                                      plan.max_context_len, plan.max_group, partition_size=psize, num_stages=nst)
+            if events is not None:
+                events[l][1].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(L_max)]
+              for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = ops.launch_count
+    e0.record()
+    for i in range(args.steps):
+        step(events[i])
+    e1.record()
+    gpu_launches = ops.launch_count - launches0
+    barrier()
+    clocks = sampler.stop()
+    from muxserve_b200.parallel import max_over_ranks
+    ms_step = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    attn_ms = sum(a.elapsed_time(b) for evs in events for a, b in evs) / args.steps     # all layers of a step
+    status = ops.device_status()
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        S_total = sum(b.num_seqs for b in batches)
+        achieved = sum(attn_bytes) / (attn_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * S_total / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "c3: " + C3_DESC, "block_size": BLOCK, "seed": args.seed,
+                       "pool": f"{num_blocks} blocks = {num_blocks * 8192 / 1e9:.1f} GB ({args.pool_frac:.0%} of HBM)",
+                       "items_per_launch": plan.item_offset, "layers": plan.layers,
+                       "placement": "one TP=4 rank's share per GPU; value counts each GPU's share as its own batch"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "paged_attn_kernel<mixed> (+ merge)",
+                         "algorithmic_bytes_per_step": sum(attn_bytes), "attention_ms_per_step": attn_ms,
+                         "peak_source": peak_src,
+                         "whole_path_gbs": (sum(attn_bytes) + sum(cw_bytes)) / (ms_step * 1e-3) / 1e9},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": gpu_launches, "clocks": clocks, "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
+        if args.workload == "c3":
+            raise SystemExit("--impl reference supports c2, c4, c5")
         run_reference(args)
+    elif args.workload == "c3":
+        run_native_c3(args)
     else:
         run_native(args)
 

@@ -1,0 +1,106 @@
+"""Descriptors for ONE attention launch over the decode batches of several colocated models.
+
+MuxServe runs every model in its own processes (muxserve/muxsched/scheduler.py:167-208) over one
+shared pool; block ids are globally unique because a single allocator serves all models
+(muxserve/flexstore/manager.py:397-398).  That makes a fused launch possible: an *item* is one
+(sequence, kv head) of some model, and the kernel needs per item only its context length, its first
+row in a packed q / out matrix, its group size (q heads per kv head), its softmax scale and its block
+list.  Models are ordered by layer count, deepest first, so that the models that still have layer
+``l`` always form a prefix of the item arrays and of the packed rows.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class ModelBatch:
+    """Decode batch of one model on this GPU (local head counts)."""
+    name: str
+    num_layers: int
+    num_q_heads: int
+    num_kv_heads: int
+    scale: float
+    context_lens: torch.Tensor      # int32 [S] (CPU or device)
+    block_tables: torch.Tensor      # int32 [L, S, H, max_blocks] on the device
+
+    @property
+    def group(self) -> int:
+        return self.num_q_heads // self.num_kv_heads
+
+    @property
+    def num_seqs(self) -> int:
+        return int(self.context_lens.numel())
+
+
+@dataclass
+class MixedPlan:
+    order: List[int]                 # indices into the caller's list, deepest model first
+    item_context_len: torch.Tensor   # int32 [items] device
+    item_q_row: torch.Tensor         # int32 [items]
+    item_group: torch.Tensor         # int32 [items]
+    item_scale: torch.Tensor         # float32 [items]
+    block_tables: torch.Tensor       # int32 [L_max, items, max_blocks]; rows of models without layer l unused
+    row_offset: List[int]            # first packed q row of each model (in `order`), plus the total
+    item_offset: List[int]           # first item of each model (in `order`), plus the total
+    layers: List[int]                # layer count of each model (in `order`)
+    max_group: int
+    max_context_len: int
+
+    def active(self, layer: int):
+        """(number of items, number of packed rows) that take part in `layer`."""
+        k = sum(1 for n in self.layers if n > layer)
+        return self.item_offset[k], self.row_offset[k]
+
+
+def build_mixed_plan(batches: Sequence[ModelBatch], device) -> MixedPlan:
+    order = sorted(range(len(batches)), key=lambda i: -batches[i].num_layers)
+    ctx_all, row_all, grp_all, scl_all = [], [], [], []
+    row_offset, item_offset, layers = [0], [0], []
+    max_blocks = max(b.block_tables.shape[-1] for b in batches)
+    L_max = max(b.num_layers for b in batches)
+    for i in order:
+        b = batches[i]
+        S, H, G = b.num_seqs, b.num_kv_heads, b.group
+        if b.num_q_heads % b.num_kv_heads or G > 8:
+            raise ValueError(f"{b.name}: q heads per kv head must be an integer <= 8 for the fused launch")
+        ctx = b.context_lens.cpu().numpy().astype(np.int32)
+        s_idx, h_idx = np.meshgrid(np.arange(S), np.arange(H), indexing="ij")
+        ctx_all.append(np.repeat(ctx, H))
+        row_all.append((row_offset[-1] + s_idx * b.num_q_heads + h_idx * G).reshape(-1).astype(np.int32))
+        grp_all.append(np.full(S * H, G, dtype=np.int32))
+        scl_all.append(np.full(S * H, b.scale, dtype=np.float32))
+        row_offset.append(row_offset[-1] + S * b.num_q_heads)
+        item_offset.append(item_offset[-1] + S * H)
+        layers.append(b.num_layers)
+    n_items = item_offset[-1]
+    tables = torch.zeros((L_max, n_items, max_blocks), dtype=torch.int32, device=device)
+    for k, i in enumerate(order):
+        b = batches[i]
+        bt = b.block_tables.to(device).clamp_min(0)
+        L, S, H, mb = bt.shape
+        tables[:L, item_offset[k]:item_offset[k + 1], :mb] = bt.reshape(L, S * H, mb)
+    cat = lambda xs, dt: torch.from_numpy(np.concatenate(xs)).to(dt).to(device)
+    return MixedPlan(order=order, item_context_len=cat(ctx_all, torch.int32), item_q_row=cat(row_all, torch.int32),
+                     item_group=cat(grp_all, torch.int32), item_scale=cat(scl_all, torch.float32),
+                     block_tables=tables, row_offset=row_offset, item_offset=item_offset, layers=layers,
+                     max_group=max(b.group for b in batches),
+                     max_context_len=int(max(int(b.context_lens.max()) for b in batches)))
+
+
+def pack_rows(plan: MixedPlan, per_model: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Concatenates per-model [S, Hq, D] tensors (caller's order) into the packed [rows, D] matrix."""
+    return torch.cat([per_model[i].reshape(-1, per_model[i].shape[-1]) for i in plan.order], dim=0)
+
+
+def unpack_rows(plan: MixedPlan, packed: torch.Tensor, batches: Sequence[ModelBatch]) -> List[torch.Tensor]:
+    """Views of the packed matrix per model, in the caller's order."""
+    out = [None] * len(batches)
+    for k, i in enumerate(plan.order):
+        b = batches[i]
+        out[i] = packed[plan.row_offset[k]:plan.row_offset[k + 1]].view(b.num_seqs, b.num_q_heads, packed.shape[-1])
+    return out
