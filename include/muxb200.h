@@ -42,6 +42,11 @@ typedef enum {
 
 typedef enum { MUX_DTYPE_F16 = 0, MUX_DTYPE_BF16 = 1 } mux_dtype_t;
 
+/* mux_attn_args_t.flags.  Default (0): one persistent wave of CTAs pulls work units
+ * from a queue and merges partitions in the same launch.  GRID_PER_UNIT: one CTA per
+ * (item, partition) and a second merge kernel; kept for comparison. */
+#define MUX_ATTN_GRID_PER_UNIT 1
+
 /* Bits of the device status word (mux_device_status). */
 #define MUX_DEV_BAD_BLOCK_ID 1u   /* a block id outside [0, num_blocks) was met and replaced by 0 */
 #define MUX_DEV_WAIT_TIMEOUT 2u   /* a bounded wait on a staged copy ran out */
@@ -105,8 +110,10 @@ int mux_reshape_and_cache(const mux_cache_write_args_t* args, void* cuda_stream)
  * never read (the reference leaves them uninitialised).
  *
  * Long contexts are split into partitions of partition_size tokens that are
- * combined through the caller's workspace (flash-decoding).  Sizes come from
- * mux_paged_attention_workspace_size; workspace may be NULL when that is 0.
+ * combined through the caller's workspace (flash-decoding), which also holds
+ * the launch's scheduling words.  Size (never 0 for a non-empty batch) comes
+ * from mux_paged_attention_workspace_size; contents need no initialisation and
+ * two launches that may overlap on the GPU must not share a workspace.
  * ---------------------------------------------------------------------- */
 typedef struct {
   void* out;                   /* [num_seqs, num_q_heads, head_size] */
@@ -133,6 +140,8 @@ typedef struct {
   int32_t dtype;               /* mux_dtype_t */
   int32_t partition_size;      /* tokens, multiple of block_size; 0 = library heuristic */
   int32_t num_stages;          /* depth of the shared-memory block ring (multiple of 4, <= 16); 0 = default */
+  int32_t flags;               /* MUX_ATTN_* bits, normally 0 */
+  int32_t reserved;
 } mux_attn_args_t;
 
 size_t mux_paged_attention_workspace_size(const mux_attn_args_t* args);
@@ -192,6 +201,8 @@ typedef struct {
   int32_t dtype;
   int32_t partition_size;
   int32_t num_stages;
+  int32_t flags;
+  int32_t reserved;
 } mux_attn_mixed_args_t;
 
 size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* args);

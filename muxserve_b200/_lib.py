@@ -20,7 +20,8 @@ MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 
-ABI_VERSION = 1
+ABI_VERSION = 2
+MUX_ATTN_GRID_PER_UNIT = 1
 
 
 class CacheWriteArgs(C.Structure):
@@ -53,6 +54,7 @@ class AttnArgs(C.Structure):
         ("num_seqs", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
         ("head_size", C.c_int32), ("block_size", C.c_int32), ("max_context_len", C.c_int32),
         ("dtype", C.c_int32), ("partition_size", C.c_int32), ("num_stages", C.c_int32),
+        ("flags", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -68,6 +70,7 @@ class AttnMixedArgs(C.Structure):
         ("num_items", C.c_int32), ("max_group", C.c_int32),
         ("head_size", C.c_int32), ("block_size", C.c_int32), ("max_context_len", C.c_int32),
         ("dtype", C.c_int32), ("partition_size", C.c_int32), ("num_stages", C.c_int32),
+        ("flags", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

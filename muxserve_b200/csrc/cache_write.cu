@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(kCwWarps * 32)
 cache_write_kernel(const __grid_constant__ CacheWriteParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * kCwWarps + warp;
+  griddep_wait();               // inputs may come from the previous kernel of the stream
+  griddep_launch_dependents();  // the next kernel may start being scheduled
   if (row >= (long long)p.num_tokens * p.num_heads) return;
   const int t = (int)(row / p.num_heads);
   const int h = (int)(row - (long long)t * p.num_heads);
@@ -63,14 +65,22 @@ cache_write_kernel(const __grid_constant__ CacheWriteParams p) {
 template <typename T>
 static int launch_cw(const CacheWriteParams& p, int block_size, cudaStream_t stream) {
   const long long rows = (long long)p.num_tokens * p.num_heads;
-  const unsigned grid = (unsigned)((rows + kCwWarps - 1) / kCwWarps);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((rows + kCwWarps - 1) / kCwWarps));
+  cfg.blockDim = dim3(kCwWarps * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
   if (block_size == 8)
-    cache_write_kernel<T, 8><<<grid, kCwWarps * 32, 0, stream>>>(p);
+    e = cudaLaunchKernelEx(&cfg, cache_write_kernel<T, 8>, p);
   else if (block_size == 16)
-    cache_write_kernel<T, 16><<<grid, kCwWarps * 32, 0, stream>>>(p);
+    e = cudaLaunchKernelEx(&cfg, cache_write_kernel<T, 16>, p);
   else
-    cache_write_kernel<T, 32><<<grid, kCwWarps * 32, 0, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+    e = cudaLaunchKernelEx(&cfg, cache_write_kernel<T, 32>, p);
   return e == cudaSuccess ? MUX_OK : record_cuda_error(e);
 }
 

@@ -20,159 +20,14 @@
 // un-normalised fp32 partial (acc, max, sum) to the workspace and a second
 // small kernel merges the partitions (flash-decoding).
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <mutex>
 
-#include "internal.h"
-#include "ptx.cuh"
+#include "attn_common.cuh"
+#include "attn_persistent.cuh"
 
 namespace mux {
-
-constexpr int kHeadSize = 128;
-constexpr int kConsumerWarps = 4;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;  // + producer warp
-constexpr int kMaxStages = 16;
-constexpr int kRedStride = kHeadSize + 4;  // padded row of the cross-warp reduction
-constexpr int kMaxSmemBytes = 227 * 1024;
-constexpr int kMaxDevicesTracked = 64;
-
-struct AttnParams {
-  const void* q;
-  void* out;
-  const void* kc;
-  const void* vc;
-  const int* block_tables;
-  const int* context_lens;
-  const int* head_mapping;
-  const int* item_ctx;
-  const int* item_q_row;
-  const int* item_group;
-  const float* item_scale;
-  long long q_s0, q_s1, o_s0, o_s1;  // single model: seq, head strides; mixed: s1 = row stride
-  long long bt_s0, bt_s1;            // single model: seq, head strides; mixed: s0 = item stride
-  float* ws_acc;
-  float* ws_ml;
-  unsigned* status;
-  long long num_blocks;
-  float scale;
-  int num_q_heads, num_kv_heads, group;
-  int gs;          // head columns kept in shared memory (1..8)
-  int head_tiles;  // ceil(group / 8)
-  int pb;          // partition size in blocks
-  int max_parts;
-  int max_context_len;
-  int nst;         // ring depth in tiles
-};
-
-// Shared-memory carve-up, identical on host (sizing) and device.
-struct SmemLayout {
-  int ring, s, pm, ids, info, bars, total;
-  int srow, prow;
-};
-
-__host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs, int nst) {
-  SmemLayout L;
-  const int tile = kHeadSize * block_size * 2;
-  const int P = pb * block_size;
-  L.srow = P + 8;
-  L.prow = P + 16;
-  int off = 0;
-  L.ring = off;
-  off += nst * tile;
-  L.s = off;
-  int s_bytes = gs * L.srow * 4;
-  int red_bytes = kConsumerWarps * gs * kRedStride * 4;
-  off += (s_bytes > red_bytes ? s_bytes : red_bytes);
-  off = (off + 15) & ~15;
-  L.pm = off;
-  off += 2 * gs * L.prow * 2;  // P as hi + lo planes
-  off = (off + 15) & ~15;
-  L.ids = off;
-  off += pb * 4;
-  off = (off + 15) & ~15;
-  L.info = off;
-  off += 8 * 8 + 8 * 8 + 8 * 2 * 4 + 16;  // qoff, ooff, ml, geff
-  L.bars = off;
-  off += 2 * kMaxStages * 8;
-  L.total = off;
-  return L;
-}
-
-struct ItemInfo {
-  long long qoff[8];
-  long long ooff[8];
-  float ml[8][2];
-  int geff;
-  int pad[3];
-};
-
-struct ItemDesc {
-  int ctx, G, seq, kvh;
-  float scale;
-  const int* bt_row;
-};
-
-template <bool MIXED>
-__device__ __forceinline__ ItemDesc load_item(const AttnParams& p, int item) {
-  ItemDesc d;
-  if (MIXED) {
-    d.ctx = p.item_ctx[item];
-    d.G = p.item_group[item];
-    d.scale = p.item_scale[item];
-    d.bt_row = p.block_tables + (long long)item * p.bt_s0;
-    d.seq = 0;
-    d.kvh = 0;
-  } else {
-    d.seq = item / p.num_kv_heads;
-    d.kvh = item - d.seq * p.num_kv_heads;
-    d.ctx = p.context_lens[d.seq];
-    d.G = p.group;
-    d.scale = p.scale;
-    d.bt_row = p.block_tables + (long long)d.seq * p.bt_s0 + (long long)d.kvh * p.bt_s1;
-  }
-  return d;
-}
-
-// Executed by one full warp: element offsets of the (up to 8) q / out rows of
-// this head tile, and how many of them exist.
-template <bool MIXED>
-__device__ __forceinline__ void resolve_heads(const AttnParams& p, const ItemDesc& d, int item,
-                                              int htile, ItemInfo* info, int lane) {
-  if (MIXED) {
-    if (lane < 8) {
-      long long row = (long long)p.item_q_row[item] + htile * 8 + lane;
-      info->qoff[lane] = row * p.q_s1;
-      info->ooff[lane] = row * p.o_s1;
-    }
-    if (lane == 0) info->geff = max(0, min(8, d.G - htile * 8));
-  } else if (p.head_mapping == nullptr) {
-    if (lane < 8) {
-      long long hq = (long long)d.kvh * d.G + htile * 8 + lane;
-      info->qoff[lane] = (long long)d.seq * p.q_s0 + hq * p.q_s1;
-      info->ooff[lane] = (long long)d.seq * p.o_s0 + hq * p.o_s1;
-    }
-    if (lane == 0) info->geff = max(0, min(8, d.G - htile * 8));
-  } else {
-    // General head_mapping: ordered compaction of the q heads mapped to this kv head.
-    int count = 0;
-    for (int base = 0; base < p.num_q_heads; base += 32) {
-      int hq = base + lane;
-      bool match = hq < p.num_q_heads && p.head_mapping[hq] == d.kvh;
-      unsigned bal = __ballot_sync(0xffffffffu, match);
-      int pos = count + __popc(bal & ((1u << lane) - 1u)) - htile * 8;
-      if (match && pos >= 0 && pos < 8) {
-        info->qoff[pos] = (long long)d.seq * p.q_s0 + (long long)hq * p.q_s1;
-        info->ooff[pos] = (long long)d.seq * p.o_s0 + (long long)hq * p.o_s1;
-      }
-      count += __popc(bal);
-    }
-    if (lane == 0) {
-      if (count != d.G) atomicOr(p.status, MUX_DEV_BAD_HEAD_MAPPING);
-      info->geff = max(0, min(8, count - htile * 8));
-    }
-  }
-}
 
 template <typename T, int BS, bool MIXED>
 __global__ void __launch_bounds__(kThreads)
@@ -457,8 +312,10 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
 // ------------------------------------------------------------------ host side
 
 struct Plan {
-  int pb, max_parts, gs, head_tiles, nst, smem;
-  size_t ws_acc_bytes, ws_ml_bytes;
+  bool persistent;
+  int pb, max_parts, gs, head_tiles, nst, smem, num_chunks;
+  size_t sched_bytes, ws_acc_bytes, ws_ml_bytes;
+  size_t total() const { return sched_bytes + ws_acc_bytes + ws_ml_bytes; }
 };
 
 static int default_stages(int block_size) {
@@ -469,9 +326,10 @@ static int default_stages(int block_size) {
 }
 
 static Plan make_plan(long long items, int group, int block_size, int max_context_len,
-                      int partition_size, int num_stages) {
+                      int partition_size, int num_stages, int flags) {
   Plan pl;
-  int psize = partition_size > 0 ? partition_size : 512;
+  pl.persistent = !(flags & MUX_ATTN_GRID_PER_UNIT);
+  int psize = partition_size > 0 ? partition_size : (pl.persistent ? 256 : 512);
   psize = std::max(block_size, (psize / block_size) * block_size);
   pl.pb = psize / block_size;
   pl.max_parts = std::max(1, (max_context_len + psize - 1) / psize);
@@ -482,7 +340,14 @@ static Plan make_plan(long long items, int group, int block_size, int max_contex
   // therefore never more than one phase apart.
   pl.nst = num_stages > 0 ? num_stages : default_stages(block_size);
   pl.nst = std::min(kMaxStages, std::max(kConsumerWarps, (pl.nst / kConsumerWarps) * kConsumerWarps));
-  pl.smem = smem_layout(block_size, pl.pb, pl.gs, pl.nst).total;
+  pl.num_chunks = (int)((items + 31) / 32);
+  pl.smem = pl.persistent ? psmem_layout(block_size, pl.pb, pl.gs, pl.nst, pl.num_chunks).total
+                          : smem_layout(block_size, pl.pb, pl.gs, pl.nst).total;
+  pl.sched_bytes = 0;
+  if (pl.persistent) {
+    size_t words = 2 + (size_t)items * pl.head_tiles;
+    pl.sched_bytes = (words * 8 + 255) & ~(size_t)255;
+  }
   if (pl.max_parts > 1) {
     size_t slots = (size_t)items * pl.head_tiles * pl.max_parts * pl.gs;
     pl.ws_acc_bytes = slots * kHeadSize * sizeof(float);
@@ -493,29 +358,102 @@ static Plan make_plan(long long items, int group, int block_size, int max_contex
   return pl;
 }
 
-template <typename T, int BS, bool MIXED>
-static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream) {
-  auto kern = paged_attn_kernel<T, BS, MIXED>;
+static int plan_limits(const Plan& pl, long long items) {
   if (pl.smem > kMaxSmemBytes) return MUX_ERR_BAD_SHAPE;  // partition too large for one SM
-  static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
+  if (pl.persistent) {
+    if (pl.num_chunks > kMaxChunks || pl.pb > kMaxPB) return MUX_ERR_TOO_LARGE;
+  } else if (items > 0x7fffffffLL || pl.max_parts > 65535) {
+    return MUX_ERR_BAD_SHAPE;
+  }
+  return MUX_OK;
+}
+
+// Launch tags of the persistent kernel's scheduling words; 0 is never used.
+static std::atomic<unsigned> g_epoch{1};
+
+static unsigned next_epoch() {
+  unsigned e = g_epoch.fetch_add(1, std::memory_order_relaxed);
+  while (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed);
+  return e;
+}
+
+struct DeviceInfo {
+  int sms = 0;
+};
+static int device_info(int* dev_out, DeviceInfo* info) {
+  static DeviceInfo cache[kMaxDevicesTracked];
+  static std::mutex mu;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return record_cuda_error(e);
-  if (dev < 0 || dev >= kMaxDevicesTracked || granted[dev] < pl.smem) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem);
+  if (dev < 0 || dev >= kMaxDevicesTracked) return record_cuda_error(cudaErrorInvalidDevice);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev].sms == 0) {
+    e = cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return record_cuda_error(e);
-    if (dev >= 0 && dev < kMaxDevicesTracked) granted[dev] = pl.smem;
   }
-  dim3 grid((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
-  kern<<<grid, kThreads, pl.smem, stream>>>(prm);
-  e = cudaGetLastError();
+  *dev_out = dev;
+  *info = cache[dev];
+  return MUX_OK;
+}
+
+template <typename K>
+static int ensure_smem(K kern, int smem, int dev, int* granted) {
+  if (granted[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    granted[dev] = smem;
+  }
+  return MUX_OK;
+}
+
+template <typename T, int BS, bool MIXED>
+static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream) {
+  int dev = 0;
+  DeviceInfo di;
+  int st = device_info(&dev, &di);
+  if (st != MUX_OK) return st;
+  cudaError_t e;
+  if (!pl.persistent) {
+    auto kern = paged_attn_kernel<T, BS, MIXED>;
+    static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
+    if ((st = ensure_smem(kern, pl.smem, dev, granted)) != MUX_OK) return st;
+    dim3 grid((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
+    kern<<<grid, kThreads, pl.smem, stream>>>(prm);
+    if ((e = cudaGetLastError()) != cudaSuccess) return record_cuda_error(e);
+    if (pl.max_parts > 1) {
+      dim3 mgrid((unsigned)items, (unsigned)pl.head_tiles);
+      paged_attn_merge_kernel<T, BS, MIXED><<<mgrid, kHeadSize, 0, stream>>>(prm);
+      if ((e = cudaGetLastError()) != cudaSuccess) return record_cuda_error(e);
+    }
+    return MUX_OK;
+  }
+  auto kern = paged_attn_persistent_kernel<T, BS, MIXED>;
+  static int granted[kMaxDevicesTracked] = {};
+  static int occ_smem[kMaxDevicesTracked] = {};
+  static int occ_val[kMaxDevicesTracked] = {};
+  if ((st = ensure_smem(kern, pl.smem, dev, granted)) != MUX_OK) return st;
+  if (occ_val[dev] == 0 || occ_smem[dev] != pl.smem) {
+    int occ = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, pl.smem);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    occ_val[dev] = std::max(1, occ);
+    occ_smem[dev] = pl.smem;
+  }
+  const long long upper = items * pl.head_tiles * (long long)pl.max_parts;  // bound on the unit count
+  const unsigned grid = (unsigned)std::max(1LL, std::min<long long>(upper, (long long)di.sms * occ_val[dev]));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = (size_t)pl.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, prm);
   if (e != cudaSuccess) return record_cuda_error(e);
-  if (pl.max_parts > 1) {
-    dim3 mgrid((unsigned)items, (unsigned)pl.head_tiles);
-    paged_attn_merge_kernel<T, BS, MIXED><<<mgrid, kHeadSize, 0, stream>>>(prm);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return record_cuda_error(e);
-  }
   return MUX_OK;
 }
 
@@ -533,6 +471,16 @@ static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, i
     MUX_CASE(__nv_bfloat16, 32);
   }
 #undef MUX_CASE
+}
+
+// Splits the caller's workspace into scheduling words and partials.
+static void bind_workspace(AttnParams& prm, const Plan& pl, void* workspace) {
+  char* base = static_cast<char*>(workspace);
+  prm.sched = pl.sched_bytes ? reinterpret_cast<unsigned long long*>(base) : nullptr;
+  prm.ws_acc = pl.ws_acc_bytes ? reinterpret_cast<float*>(base + pl.sched_bytes) : nullptr;
+  prm.ws_ml = pl.ws_ml_bytes ? reinterpret_cast<float*>(base + pl.sched_bytes + pl.ws_acc_bytes) : nullptr;
+  prm.epoch = pl.persistent ? next_epoch() : 0u;
+  prm.num_chunks = pl.num_chunks;
 }
 
 static int check_common(int dtype, int head_size, int block_size) {
@@ -582,16 +530,30 @@ static int validate(const mux_attn_mixed_args_t* a) {
   return MUX_OK;
 }
 
+static Plan plan_of(const mux_attn_args_t* a) {
+  return make_plan((long long)a->num_seqs * a->num_kv_heads, a->num_q_heads / a->num_kv_heads,
+                   a->block_size, a->max_context_len, a->partition_size, a->num_stages, a->flags);
+}
+
+static Plan plan_of(const mux_attn_mixed_args_t* a) {
+  return make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len, a->partition_size,
+                   a->num_stages, a->flags);
+}
+
+static int check_workspace(const Plan& pl, const void* workspace, size_t workspace_bytes) {
+  const size_t need = pl.total();
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return MUX_ERR_WORKSPACE_TOO_SMALL;
+  if (need > 0 && !aligned16(workspace)) return MUX_ERR_MISALIGNED;
+  return MUX_OK;
+}
+
 }  // namespace mux
 
 extern "C" {
 
 size_t mux_paged_attention_workspace_size(const mux_attn_args_t* a) {
   if (mux::validate(a) != MUX_OK || a->num_seqs == 0) return 0;
-  mux::Plan pl = mux::make_plan((long long)a->num_seqs * a->num_kv_heads,
-                                a->num_q_heads / a->num_kv_heads, a->block_size,
-                                a->max_context_len, a->partition_size, a->num_stages);
-  return pl.ws_acc_bytes + pl.ws_ml_bytes;
+  return mux::plan_of(a).total();
 }
 
 int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t workspace_bytes,
@@ -600,13 +562,9 @@ int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t worksp
   if (st != MUX_OK) return st;
   if (a->num_seqs == 0) return MUX_OK;
   const long long items = (long long)a->num_seqs * a->num_kv_heads;
-  const int group = a->num_q_heads / a->num_kv_heads;
-  mux::Plan pl = mux::make_plan(items, group, a->block_size, a->max_context_len,
-                                a->partition_size, a->num_stages);
-  const size_t need = pl.ws_acc_bytes + pl.ws_ml_bytes;
-  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return MUX_ERR_WORKSPACE_TOO_SMALL;
-  if (need > 0 && !mux::aligned16(workspace)) return MUX_ERR_MISALIGNED;
-  if (items > 0x7fffffffLL || pl.max_parts > 65535) return MUX_ERR_BAD_SHAPE;
+  const mux::Plan pl = mux::plan_of(a);
+  if ((st = mux::plan_limits(pl, items)) != MUX_OK) return st;
+  if ((st = mux::check_workspace(pl, workspace, workspace_bytes)) != MUX_OK) return st;
   unsigned* status = mux::device_status_ptr();
   if (status == nullptr) return MUX_ERR_CUDA;
 
@@ -624,30 +582,27 @@ int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t worksp
   prm.o_s1 = a->out_head_stride;
   prm.bt_s0 = a->bt_seq_stride;
   prm.bt_s1 = a->bt_head_stride;
-  prm.ws_acc = static_cast<float*>(workspace);
-  prm.ws_ml = need > 0 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.ws_acc_bytes)
-                       : nullptr;
   prm.status = status;
   prm.num_blocks = a->num_blocks;
   prm.scale = a->scale;
   prm.num_q_heads = a->num_q_heads;
   prm.num_kv_heads = a->num_kv_heads;
-  prm.group = group;
+  prm.group = a->num_q_heads / a->num_kv_heads;
   prm.gs = pl.gs;
   prm.head_tiles = pl.head_tiles;
   prm.pb = pl.pb;
   prm.max_parts = pl.max_parts;
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
+  prm.num_items = (int)items;
+  mux::bind_workspace(prm, pl, workspace);
   return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
                             static_cast<cudaStream_t>(cuda_stream));
 }
 
 size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* a) {
   if (mux::validate(a) != MUX_OK || a->num_items == 0) return 0;
-  mux::Plan pl = mux::make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len,
-                                a->partition_size, a->num_stages);
-  return pl.ws_acc_bytes + pl.ws_ml_bytes;
+  return mux::plan_of(a).total();
 }
 
 int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
@@ -655,12 +610,9 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
   int st = mux::validate(a);
   if (st != MUX_OK) return st;
   if (a->num_items == 0) return MUX_OK;
-  mux::Plan pl = mux::make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len,
-                                a->partition_size, a->num_stages);
-  const size_t need = pl.ws_acc_bytes + pl.ws_ml_bytes;
-  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return MUX_ERR_WORKSPACE_TOO_SMALL;
-  if (need > 0 && !mux::aligned16(workspace)) return MUX_ERR_MISALIGNED;
-  if (pl.max_parts > 65535) return MUX_ERR_BAD_SHAPE;
+  const mux::Plan pl = mux::plan_of(a);
+  if ((st = mux::plan_limits(pl, a->num_items)) != MUX_OK) return st;
+  if ((st = mux::check_workspace(pl, workspace, workspace_bytes)) != MUX_OK) return st;
   unsigned* status = mux::device_status_ptr();
   if (status == nullptr) return MUX_ERR_CUDA;
 
@@ -677,9 +629,6 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
   prm.q_s1 = a->q_row_stride;
   prm.o_s1 = a->out_row_stride;
   prm.bt_s0 = a->bt_item_stride;
-  prm.ws_acc = static_cast<float*>(workspace);
-  prm.ws_ml = need > 0 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.ws_acc_bytes)
-                       : nullptr;
   prm.status = status;
   prm.num_blocks = a->num_blocks;
   prm.gs = pl.gs;
@@ -688,6 +637,8 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
   prm.max_parts = pl.max_parts;
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
+  prm.num_items = a->num_items;
+  mux::bind_workspace(prm, pl, workspace);
   return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
                            static_cast<cudaStream_t>(cuda_stream));
 }
@@ -701,9 +652,10 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
 // serving worker whose memory budget was fixed at start-up (FlexStore gives the
 // KV pool a set fraction of HBM and the rest is spoken for), a process that
 // shares the GPU with others under MPS and must not grow, or code on a path
-// where allocation calls are simply not allowed.  For them the split-K scratch
-// lives in a fixed array inside the library image instead of a caller buffer.
-// Every GPU that loads the library carries the array until the process exits.
+// where allocation calls are simply not allowed.  For them the scratch of the
+// launch (scheduling words and flash-decoding partials) lives in a fixed array
+// inside the library image instead of a caller buffer.  Every GPU that loads the
+// library carries the array until the process exits.
 namespace mux {
 
 constexpr size_t kStaticScratchBytes = MUX_STATIC_SCRATCH_BYTES;
@@ -742,7 +694,8 @@ extern "C" int mux_paged_attention_static_scratch(const mux_attn_args_t* a, void
   void* scratch = nullptr;
   st = mux::static_scratch_address(&scratch);
   if (st != MUX_OK) return st;
-  // Nothing in the scratch has to start at zero: every partial that the merge
-  // kernel reads is written by the attention kernel of the same call first.
+  // Nothing in the scratch has to be cleared by the caller: scheduling words
+  // carry a per-launch tag and are put back to zero by the kernel itself, and
+  // every partial that is read was written earlier in the same launch.
   return mux_paged_attention(a, scratch, mux::kStaticScratchBytes, cuda_stream);
 }

@@ -46,13 +46,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  When the limit runs out the caller's status word gets
 // `timeout_bit` and the wait returns as if it had succeeded, so that every
 // later barrier of the CTA is still reached and the kernel ends; the result of
-// that CTA is then garbage and the host learns it from the status word.
-constexpr uint32_t kWaitLimit = 1u << 22;
+// that CTA is then garbage and the host learns it from the status word.  Once
+// the bit is set (by any CTA) every other wait gives up after kWaitRecheck
+// polls, so a protocol error costs one expiry, not one per wait.
+constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr uint32_t kWaitRecheck = 1u << 10;
 
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, unsigned* status,
                                           unsigned timeout_bit) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return;
+    if ((i & (kWaitRecheck - 1)) == kWaitRecheck - 1 &&
+        (*reinterpret_cast<volatile unsigned*>(status) & timeout_bit))
+      return;
   }
   atomicOr(status, timeout_bit);
 }
@@ -80,6 +86,14 @@ __device__ __forceinline__ uint64_t l2_evict_first_policy() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
   return pol;
+}
+
+// Programmatic dependent launch: `wait` blocks until every kernel this launch
+// depends on has completed and its writes are visible; `launch_dependents`
+// lets the next kernel of the stream start being scheduled.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {

@@ -130,7 +130,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                     value_cache: torch.Tensor, head_mapping: Optional[torch.Tensor], scale: float,
                     block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
                     max_context_len: int, *, num_kv_heads: Optional[int] = None,
-                    partition_size: int = 0, num_stages: int = 0) -> None:
+                    partition_size: int = 0, num_stages: int = 0, flags: int = 0) -> None:
     """Decode attention of one query token per sequence over the paged pool.
 
     ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
@@ -187,14 +187,14 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(),
         scale=float(scale), num_seqs=S, num_q_heads=Hq, num_kv_heads=H, head_size=HEAD_SIZE,
         block_size=block_size, max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages)
+        partition_size=partition_size, num_stages=num_stages, flags=flags)
     L = lib()
     need = L.mux_paged_attention_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
     check(L.mux_paged_attention(C.byref(args), ws.data_ptr() if ws is not None else None,
                                 ws.numel() if ws is not None else 0, _stream()), "paged_attention")
     global launch_count
-    launch_count += 0 if S == 0 else (2 if need > 0 else 1)
+    launch_count += 0 if S == 0 else (2 if (flags & _lib.MUX_ATTN_GRID_PER_UNIT) and max_context_len > (partition_size or 512) else 1)
 
 
 def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
@@ -202,7 +202,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                           item_context_len: torch.Tensor, item_q_row: torch.Tensor,
                           item_group: torch.Tensor, item_scale: torch.Tensor, block_size: int,
                           max_context_len: int, max_group: int, *, partition_size: int = 0,
-                          num_stages: int = 0) -> None:
+                          num_stages: int = 0, flags: int = 0) -> None:
     """One launch for the decode batches of several models sharing the pool.
 
     Item ``i`` is one (sequence, kv head) of some model: q rows
@@ -238,7 +238,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
         item_group=item_group.data_ptr(), item_scale=item_scale.data_ptr(),
         num_items=n, max_group=max_group, head_size=HEAD_SIZE, block_size=block_size,
         max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages)
+        partition_size=partition_size, num_stages=num_stages, flags=flags)
     L = lib()
     need = L.mux_paged_attention_mixed_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
@@ -246,7 +246,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                                       ws.numel() if ws is not None else 0, _stream()),
           "paged_attention_mixed")
     global launch_count
-    launch_count += 0 if n == 0 else (2 if need > 0 else 1)
+    launch_count += 0 if n == 0 else (2 if (flags & _lib.MUX_ATTN_GRID_PER_UNIT) and max_context_len > (partition_size or 512) else 1)
 
 
 def device_status() -> int:

@@ -59,7 +59,11 @@ def test_validation_happens_before_any_launch(built_lib):
     assert L.mux_paged_attention(C.byref(a), None, 0, None) == -5          # misaligned q
     a.q, a.max_context_len, a.partition_size = 0x1000, 4096, 512
     need = L.mux_paged_attention_workspace_size(C.byref(a))
-    assert need == (4 * 4) * 8 * 3 * (128 + 2) * 4                          # items x partitions x group x (acc + m,l) fp32
+    partials = (4 * 4) * 8 * 3 * (128 + 2) * 4                              # items x partitions x group x (acc + m,l) fp32
+    assert need == 256 + partials                                           # + scheduling words (2 + items, 8 B each, padded)
+    a.flags = _lib.MUX_ATTN_GRID_PER_UNIT
+    assert L.mux_paged_attention_workspace_size(C.byref(a)) == partials
+    a.flags = 0
     assert L.mux_paged_attention(C.byref(a), None, 0, None) == -8          # workspace missing
     a.partition_size = 100
     assert L.mux_paged_attention(C.byref(a), None, 0, None) == -6          # not a multiple of block_size

@@ -27,28 +27,30 @@ def run(ops, gu, case, kc, vc, head_mapping=None, **kw):
     return out
 
 
+@pytest.mark.parametrize("flags", [0, 1], ids=["persistent", "grid_per_unit"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B", [16, 8, 32])
 @pytest.mark.parametrize("group", [1, 8])
-def test_attention_ragged(env, dtype, B, group):
+def test_attention_ragged(env, dtype, B, group, flags):
     ops, gu = env
     ctx = [1, 2, B - 1, B, B + 1, 255, 256, 257, 300, 511, 77, 1000]
     H = 3
     case, kc, vc = gu.make_case(len(ctx), H * group, H, ctx, B, dtype, seed=3 + B + group, num_blocks=2048)
-    out = run(ops, gu, case, kc, vc)
+    out = run(ops, gu, case, kc, vc, flags=flags)
     kc_c, vc_c, ref = gu.oracle_step(case, kc, vc)
     assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
     gu.assert_close(out, ref, f"B={B} G={group} {dtype}")
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("flags", [0, 1], ids=["persistent", "grid_per_unit"])
 @pytest.mark.parametrize("psize,stages", [(16, 4), (64, 4), (128, 8), (512, 8), (1024, 12), (4096, 16)])
-def test_attention_partition_sizes(env, psize, stages):
+def test_attention_partition_sizes(env, psize, stages, flags):
     """Every partitioning gives the same answer (single partition up to 63 partitions per sequence)."""
     ops, gu = env
     ctx = [1000, 17, 513, 64, 2, 999]
     case, kc, vc = gu.make_case(len(ctx), 4, 4, ctx, 16, torch.float16, seed=21, num_blocks=1024)
-    out = run(ops, gu, case, kc, vc, partition_size=psize, num_stages=stages)
+    out = run(ops, gu, case, kc, vc, partition_size=psize, num_stages=stages, flags=flags)
     _, _, ref = gu.oracle_step(case, kc, vc)
     gu.assert_close(out, ref, f"partition {psize}")
     assert ops.device_status() == 0
@@ -162,6 +164,20 @@ def test_attention_known_answers(env):
     from oracle.attention_oracle import gather_kv
     _, v = gather_kv(kc.cpu(), vc.cpu(), case.block_tables[0, 2, 1, :17].cpu(), 257)
     assert torch.allclose(out[2, 4].float().cpu(), v.mean(0), atol=2e-3, rtol=1e-2)
+
+
+def test_attention_many_units_per_cta_and_repeated_launches(env):
+    """More work units than resident CTAs (every CTA loops over many units) and back-to-back launches
+    on one workspace: scheduling words must come back clean each time."""
+    ops, gu = env
+    gen = torch.Generator().manual_seed(5)
+    ctx = torch.randint(1, 400, (192,), generator=gen).tolist()
+    case, kc, vc = gu.make_case(len(ctx), 8, 8, ctx, 16, torch.float16, seed=77, num_blocks=40000)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    for rep in range(3):
+        out = run(ops, gu, case, kc, vc, partition_size=32)          # ~ 10k units on ~ 900 CTAs
+        gu.assert_close(out, ref, f"repeat {rep}")
+    assert ops.device_status() == 0
 
 
 def test_attention_edge_cases(env):
