@@ -63,6 +63,7 @@ def parse_args():
     ap.add_argument("--pool-frac", type=float, default=0.6, help="fraction of HBM given to the KV pool")
     ap.add_argument("--partition-size", type=int, default=0)
     ap.add_argument("--num-stages", type=int, default=0)
+    ap.add_argument("--attn-flags", type=int, default=0, help="MUX_ATTN_* bits passed to paged_attention (1 = persistent kernel)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiler captures)")
     ap.add_argument("--seed", type=int, default=20240531)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -281,7 +282,7 @@ def run_native(args):
         if ev is not None:
             ev[0].record()
         ops.paged_attention(out, case.q[r], kc, vc, None, case.scale, case.block_tables[r], case.context_lens,
-                            BLOCK, case.max_context_len, partition_size=psize, num_stages=nst)
+                            BLOCK, case.max_context_len, partition_size=psize, num_stages=nst, flags=args.attn_flags)
         if ev is not None:
             ev[1].record()
 

@@ -42,10 +42,16 @@ typedef enum {
 
 typedef enum { MUX_DTYPE_F16 = 0, MUX_DTYPE_BF16 = 1 } mux_dtype_t;
 
-/* mux_attn_args_t.flags.  Default (0): one persistent wave of CTAs pulls work units
- * from a queue and merges partitions in the same launch.  GRID_PER_UNIT: one CTA per
- * (item, partition) and a second merge kernel; kept for comparison. */
-#define MUX_ATTN_GRID_PER_UNIT 1
+/* mux_attn_args_t.flags.  Default (0): one CTA per (item, partition) and a small second
+ * kernel that merges the partitions.  PERSISTENT: one wave of CTAs pulls work units from a
+ * queue and the last partition of an item to finish merges them in the same launch (one
+ * launch instead of two; measured slower on large batches). */
+#define MUX_ATTN_PERSISTENT 1
+/* The leading mux_*_workspace_size bytes' scheduling words are known to be zero: the
+ * workspace was zero-filled once and has since been used only by these calls (which leave
+ * it zero-filled).  Without this flag the words are cleared on the stream before each
+ * launch.  After a non-zero mux_device_status treat the workspace as dirty again. */
+#define MUX_ATTN_WORKSPACE_CLEAN 2
 
 /* Bits of the device status word (mux_device_status). */
 #define MUX_DEV_BAD_BLOCK_ID 1u   /* a block id outside [0, num_blocks) was met and replaced by 0 */
@@ -112,8 +118,9 @@ int mux_reshape_and_cache(const mux_cache_write_args_t* args, void* cuda_stream)
  * Long contexts are split into partitions of partition_size tokens that are
  * combined through the caller's workspace (flash-decoding), which also holds
  * the launch's scheduling words.  Size (never 0 for a non-empty batch) comes
- * from mux_paged_attention_workspace_size; contents need no initialisation and
- * two launches that may overlap on the GPU must not share a workspace.
+ * from mux_paged_attention_workspace_size; contents need no initialisation
+ * (but see MUX_ATTN_WORKSPACE_CLEAN) and two launches that may overlap on the
+ * GPU must not share a workspace.
  * ---------------------------------------------------------------------- */
 typedef struct {
   void* out;                   /* [num_seqs, num_q_heads, head_size] */

@@ -21,7 +21,8 @@ MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 
 ABI_VERSION = 2
-MUX_ATTN_GRID_PER_UNIT = 1
+MUX_ATTN_PERSISTENT = 1
+MUX_ATTN_WORKSPACE_CLEAN = 2
 
 
 class CacheWriteArgs(C.Structure):

@@ -44,8 +44,7 @@ struct AttnParams {
   int max_context_len;
   int nst;         // ring depth in tiles
   // persistent kernel only
-  unsigned long long* sched;  // [0] unit queue, [1] exit count, [2 + item*head_tiles + tile] merge tickets
-  unsigned epoch;             // tag of this launch in the high half of every sched word
+  unsigned* sched;            // [0] unit queue, [1] exit count, [2 + item*head_tiles + tile] merge tickets
   int num_items;
   int num_chunks;             // ceil(num_items / 32)
 };

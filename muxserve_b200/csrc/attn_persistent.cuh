@@ -9,10 +9,11 @@
 // The last unit of an item to finish (a ticket counter per item, no spinning)
 // merges the item's partitions, so one launch does all of attention.
 //
-// Queue, exit and ticket words are 64-bit: the high half carries the launch's
-// epoch, so words left by earlier launches (or never initialised) read as zero;
-// the last CTA to leave and the merging unit put their words back to zero, so a
-// replay of the same launch (same epoch) also starts clean.
+// Queue, exit and ticket words are plain 32-bit counters advanced with
+// atomicAdd (a compare-and-swap loop on one hot word completes only one
+// increment per round trip when hundreds of CTAs contend).  They must be zero
+// when the kernel starts; the merging unit and the last CTA to leave put them
+// back to zero, so a clean workspace stays clean from launch to launch.
 #pragma once
 #include "attn_common.cuh"
 
@@ -20,7 +21,10 @@ namespace mux {
 
 constexpr int kMaxChunks = 1024;   // 32 items each: at most 32768 items per launch
 constexpr int kMaxPB = 256;        // blocks per partition
-constexpr unsigned kCasLimit = 1u << 20;
+constexpr int kMaxTickets = 65536; // (item, head tile) pairs per launch
+// The scheduling words sit at the front of the workspace in a region of fixed size, so that
+// the partials behind them never overlap words of a launch with another shape.
+constexpr size_t kSchedBytes = ((2 + (size_t)kMaxTickets) * 4 + 255) & ~(size_t)255;
 
 struct UnitDesc {
   ItemInfo info;        // q / out row offsets of the head tile, (max, sum) per head, geff
@@ -28,8 +32,17 @@ struct UnitDesc {
   int item;             // < 0: no more work
   int htile, part, nparts, ntok, nblk;
   float scale;
-  int ids[kMaxPB];
+  int ids[1];           // pb entries follow (the descriptor stride is desc_stride(pb))
 };
+
+// A descriptor slot = header + pb block ids, then the unit's q rows (gs x 128 elements),
+// which the producer stages with bulk copies so that the consumers never wait on global memory.
+__host__ __device__ inline int desc_q_offset(int pb) {
+  return ((int)sizeof(UnitDesc) + (pb - 1) * 4 + 15) & ~15;
+}
+__host__ __device__ inline int desc_stride(int pb, int gs) {
+  return desc_q_offset(pb) + gs * kHeadSize * 2;
+}
 
 struct PSmemLayout {
   int ring, s, pm, desc, cum, flag, bars, total;
@@ -54,7 +67,7 @@ __host__ __device__ inline PSmemLayout psmem_layout(int block_size, int pb, int 
   off += 2 * gs * L.prow * 2;
   off = (off + 15) & ~15;
   L.desc = off;
-  off += 2 * (int)sizeof(UnitDesc);
+  off += 2 * desc_stride(pb, gs);
   L.cum = off;
   off += (num_chunks + 1) * 4;
   off = (off + 15) & ~15;
@@ -64,24 +77,6 @@ __host__ __device__ inline PSmemLayout psmem_layout(int block_size, int pb, int 
   off += (2 * kMaxStages + 4) * 8;
   L.total = off;
   return L;
-}
-
-// Adds one to an epoch-tagged counter and returns its previous value (0 when the
-// word belongs to another epoch).  Lock-free; the retry bound only guards
-// against a corrupted word.
-__device__ __forceinline__ unsigned counter_inc(unsigned long long* word, unsigned epoch,
-                                                unsigned* status) {
-  unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(word);
-  for (unsigned i = 0; i < kCasLimit; ++i) {
-    const bool fresh = static_cast<unsigned>(seen >> 32) != epoch;
-    const unsigned long long want =
-        fresh ? ((static_cast<unsigned long long>(epoch) << 32) | 1ull) : seen + 1ull;
-    const unsigned long long got = atomicCAS(word, seen, want);
-    if (got == seen) return fresh ? 0u : static_cast<unsigned>(seen);
-    seen = got;
-  }
-  atomicOr(status, MUX_DEV_WAIT_TIMEOUT);
-  return 0xffffffffu;
 }
 
 template <bool MIXED>
@@ -111,7 +106,9 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
   const int P = p.pb * BS;
   const int nst = p.nst;
   const PSmemLayout L = psmem_layout(BS, p.pb, p.gs, nst, p.num_chunks);
-  UnitDesc* desc = reinterpret_cast<UnitDesc*>(smem + L.desc);
+  unsigned char* desc_base = smem + L.desc;
+  const int dstride = desc_stride(p.pb, p.gs);
+  const int dq_off = desc_q_offset(p.pb);
   unsigned* cum = reinterpret_cast<unsigned*>(smem + L.cum);   // cum[c] = units before chunk c
   int* flag = reinterpret_cast<int*>(smem + L.flag);
   const uint32_t bars = smem_u32(smem + L.bars);
@@ -164,15 +161,16 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
     // ------------------------------ producer warp ------------------------------
     const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
     const unsigned char* vc = static_cast<const unsigned char*>(p.vc);
+    unsigned u_next = 0;               // next unit of this CTA (lane 0)
     unsigned pos = 0;                  // next ring stage (lane 0)
     unsigned e_used = 0, e_par = 0;    // per stage: used before / parity of the next empty wait (lane 0)
     for (unsigned k = 0;; ++k) {
       const int slot = k & 1;
-      UnitDesc* d = desc + slot;
+      UnitDesc* d = reinterpret_cast<UnitDesc*>(desc_base + slot * dstride);
       if (k >= 2) mbar_wait(bar_dempty + 8 * slot, ((k >> 1) - 1) & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
-      unsigned u = 0;
-      if (lane == 0) u = counter_inc(p.sched, p.epoch, p.status);
-      u = __shfl_sync(0xffffffffu, u, 0);
+      // the first unit of a CTA is its own index; later ones come from the queue (taken by
+      // lane 0 one unit early, so the round trip overlaps the previous unit's copies)
+      const unsigned u = k == 0 ? blockIdx.x : __shfl_sync(0xffffffffu, u_next, 0);
       if (u >= U) {
         if (lane == 0) {
           d->item = -1;
@@ -232,7 +230,18 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
       }
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(bar_dfull + 8 * slot);
+        // publish the descriptor; the unit's q rows (256 B each) ride on the same barrier
+        const int gq = nblk > 0 ? d->info.geff : 0;
+        if (gq > 0) {
+          mbar_arrive_expect_tx(bar_dfull + 8 * slot, gq * kHeadSize * 2);
+          const uint32_t qdst = smem_u32(reinterpret_cast<unsigned char*>(d) + dq_off);
+          for (int n = 0; n < gq; ++n)
+            bulk_g2s(qdst + n * kHeadSize * 2, static_cast<const T*>(p.q) + d->info.qoff[n], kHeadSize * 2,
+                     bar_dfull + 8 * slot);
+        } else {
+          mbar_arrive(bar_dfull + 8 * slot);
+        }
+        u_next = gridDim.x + atomicAdd(p.sched, 1u);
         // K blocks, then V blocks.  Each phase starts on a ring position that is a multiple
         // of 4, so block j of a phase always sits in a stage congruent to j mod 4 and is
         // consumed by warp j mod 4: a stage has one fixed consumer warp.
@@ -272,7 +281,7 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
 
   for (unsigned k = 0;; ++k) {
     const int slot = k & 1;
-    UnitDesc* d = desc + slot;
+    UnitDesc* d = reinterpret_cast<UnitDesc*>(desc_base + slot * dstride);
     mbar_wait(bar_dfull + 8 * slot, (k >> 1) & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
     if (d->item < 0) break;
     ItemInfo* info = &d->info;
@@ -286,11 +295,11 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
     } else if (geff > 0) {
       uint32_t qf[8][2];
       if (g < geff) {
-        const T* qr = static_cast<const T*>(p.q) + info->qoff[g];
+        const T* qr = reinterpret_cast<const T*>(reinterpret_cast<const unsigned char*>(d) + dq_off) + g * kHeadSize;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          qf[ks][0] = ldg32_nc(qr + ks * 16 + 2 * tq);
-          qf[ks][1] = ldg32_nc(qr + ks * 16 + 8 + 2 * tq);
+          qf[ks][0] = *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 2 * tq);
+          qf[ks][1] = *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8 + 2 * tq);
         }
       } else {
 #pragma unroll
@@ -450,10 +459,10 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
         __threadfence();
         named_bar_sync(1, kConsumerThreads);
         if (tid == 0) {
-          unsigned long long* ticket = p.sched + 2 + ((long long)d->item * p.head_tiles + d->htile);
-          const unsigned tk = counter_inc(ticket, p.epoch, p.status);
+          unsigned* ticket = p.sched + 2 + ((long long)d->item * p.head_tiles + d->htile);
+          const unsigned tk = atomicAdd(ticket, 1u);
           const int last = tk == (unsigned)(nparts - 1);
-          if (last) *ticket = 0ull;  // nobody else touches it any more in this launch
+          if (last) *ticket = 0u;  // nobody else touches it any more in this launch
           *flag = last;
         }
         named_bar_sync(1, kConsumerThreads);
@@ -480,10 +489,10 @@ paged_attn_persistent_kernel(const __grid_constant__ AttnParams p) {
 
   // The last CTA to leave clears the queue and exit words for the next launch.
   if (tid == 0) {
-    const unsigned gone = counter_inc(p.sched + 1, p.epoch, p.status);
+    const unsigned gone = atomicAdd(p.sched + 1, 1u);
     if (gone == gridDim.x - 1) {
-      p.sched[0] = 0ull;
-      p.sched[1] = 0ull;
+      p.sched[0] = 0u;
+      p.sched[1] = 0u;
     }
   }
 }

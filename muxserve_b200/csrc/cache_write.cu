@@ -75,6 +75,15 @@ static int launch_cw(const CacheWriteParams& p, int block_size, cudaStream_t str
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
+  // Same shared-memory carve-out as the attention kernel that follows, so that the SMs are
+  // not reconfigured between the two launches.
+  static bool carve = false;
+  if (!carve) {
+    cudaFuncSetAttribute(cache_write_kernel<T, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(cache_write_kernel<T, 16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(cache_write_kernel<T, 32>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    carve = true;
+  }
   if (block_size == 8)
     e = cudaLaunchKernelEx(&cfg, cache_write_kernel<T, 8>, p);
   else if (block_size == 16)

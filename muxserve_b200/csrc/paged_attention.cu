@@ -20,7 +20,6 @@
 // un-normalised fp32 partial (acc, max, sum) to the workspace and a second
 // small kernel merges the partitions (flash-decoding).
 #include <algorithm>
-#include <atomic>
 #include <cstdint>
 #include <mutex>
 
@@ -43,6 +42,8 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   const int item = blockIdx.x, part = blockIdx.y, htile = blockIdx.z;
   const int P = p.pb * BS;
 
+  griddep_wait();               // inputs may be written by the previous kernel of the stream
+  griddep_launch_dependents();  // the next kernel may start being scheduled behind this grid
   ItemDesc d = load_item<MIXED>(p, item);
   if (d.ctx < 0 || d.ctx > p.max_context_len) {
     if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
@@ -285,6 +286,8 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
   const int item = blockIdx.x, htile = blockIdx.y;
   const int tid = threadIdx.x;
   const int P = p.pb * BS;
+  griddep_wait();
+  griddep_launch_dependents();
   ItemDesc d = load_item<MIXED>(p, item);
   if (d.ctx < 0) d.ctx = 0;
   if (d.ctx > p.max_context_len) d.ctx = p.max_context_len;
@@ -328,7 +331,7 @@ static int default_stages(int block_size) {
 static Plan make_plan(long long items, int group, int block_size, int max_context_len,
                       int partition_size, int num_stages, int flags) {
   Plan pl;
-  pl.persistent = !(flags & MUX_ATTN_GRID_PER_UNIT);
+  pl.persistent = (flags & MUX_ATTN_PERSISTENT) != 0;
   int psize = partition_size > 0 ? partition_size : (pl.persistent ? 256 : 512);
   psize = std::max(block_size, (psize / block_size) * block_size);
   pl.pb = psize / block_size;
@@ -343,11 +346,7 @@ static Plan make_plan(long long items, int group, int block_size, int max_contex
   pl.num_chunks = (int)((items + 31) / 32);
   pl.smem = pl.persistent ? psmem_layout(block_size, pl.pb, pl.gs, pl.nst, pl.num_chunks).total
                           : smem_layout(block_size, pl.pb, pl.gs, pl.nst).total;
-  pl.sched_bytes = 0;
-  if (pl.persistent) {
-    size_t words = 2 + (size_t)items * pl.head_tiles;
-    pl.sched_bytes = (words * 8 + 255) & ~(size_t)255;
-  }
+  pl.sched_bytes = kSchedBytes;  // same layout for both launch schemes
   if (pl.max_parts > 1) {
     size_t slots = (size_t)items * pl.head_tiles * pl.max_parts * pl.gs;
     pl.ws_acc_bytes = slots * kHeadSize * sizeof(float);
@@ -361,20 +360,12 @@ static Plan make_plan(long long items, int group, int block_size, int max_contex
 static int plan_limits(const Plan& pl, long long items) {
   if (pl.smem > kMaxSmemBytes) return MUX_ERR_BAD_SHAPE;  // partition too large for one SM
   if (pl.persistent) {
-    if (pl.num_chunks > kMaxChunks || pl.pb > kMaxPB) return MUX_ERR_TOO_LARGE;
+    if (pl.num_chunks > kMaxChunks || pl.pb > kMaxPB || items * pl.head_tiles > kMaxTickets)
+      return MUX_ERR_TOO_LARGE;
   } else if (items > 0x7fffffffLL || pl.max_parts > 65535) {
     return MUX_ERR_BAD_SHAPE;
   }
   return MUX_OK;
-}
-
-// Launch tags of the persistent kernel's scheduling words; 0 is never used.
-static std::atomic<unsigned> g_epoch{1};
-
-static unsigned next_epoch() {
-  unsigned e = g_epoch.fetch_add(1, std::memory_order_relaxed);
-  while (e == 0) e = g_epoch.fetch_add(1, std::memory_order_relaxed);
-  return e;
 }
 
 struct DeviceInfo {
@@ -418,13 +409,30 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
     auto kern = paged_attn_kernel<T, BS, MIXED>;
     static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
     if ((st = ensure_smem(kern, pl.smem, dev, granted)) != MUX_OK) return st;
-    dim3 grid((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
-    kern<<<grid, kThreads, pl.smem, stream>>>(prm);
-    if ((e = cudaGetLastError()) != cudaSuccess) return record_cuda_error(e);
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)pl.smem;
+    cfg.stream = stream;
+    cfg.attrs = pdl;
+    cfg.numAttrs = 1;
+    if ((e = cudaLaunchKernelEx(&cfg, kern, prm)) != cudaSuccess) return record_cuda_error(e);
     if (pl.max_parts > 1) {
       dim3 mgrid((unsigned)items, (unsigned)pl.head_tiles);
-      paged_attn_merge_kernel<T, BS, MIXED><<<mgrid, kHeadSize, 0, stream>>>(prm);
-      if ((e = cudaGetLastError()) != cudaSuccess) return record_cuda_error(e);
+      static bool carve[kMaxDevicesTracked] = {};
+      if (!carve[dev]) {  // same shared-memory carve-out as the main kernel: no SM reconfiguration between them
+        cudaFuncSetAttribute(paged_attn_merge_kernel<T, BS, MIXED>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        carve[dev] = true;
+      }
+      cfg.gridDim = mgrid;
+      cfg.blockDim = dim3(kHeadSize);
+      cfg.dynamicSmemBytes = 0;
+      if ((e = cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel<T, BS, MIXED>, prm)) != cudaSuccess)
+        return record_cuda_error(e);
     }
     return MUX_OK;
   }
@@ -476,10 +484,9 @@ static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, i
 // Splits the caller's workspace into scheduling words and partials.
 static void bind_workspace(AttnParams& prm, const Plan& pl, void* workspace) {
   char* base = static_cast<char*>(workspace);
-  prm.sched = pl.sched_bytes ? reinterpret_cast<unsigned long long*>(base) : nullptr;
+  prm.sched = pl.sched_bytes ? reinterpret_cast<unsigned*>(base) : nullptr;
   prm.ws_acc = pl.ws_acc_bytes ? reinterpret_cast<float*>(base + pl.sched_bytes) : nullptr;
   prm.ws_ml = pl.ws_ml_bytes ? reinterpret_cast<float*>(base + pl.sched_bytes + pl.ws_acc_bytes) : nullptr;
-  prm.epoch = pl.persistent ? next_epoch() : 0u;
   prm.num_chunks = pl.num_chunks;
 }
 
@@ -504,8 +511,8 @@ static int validate(const mux_attn_args_t* a) {
     return MUX_ERR_NULL_POINTER;
   if (!aligned16(a->key_cache) || !aligned16(a->value_cache) || !aligned16(a->q) || !aligned16(a->out))
     return MUX_ERR_MISALIGNED;
-  // q rows are read as 32-bit pairs, out rows written per element: 4-byte rule on strides.
-  if ((a->q_seq_stride & 1) || (a->q_head_stride & 1)) return MUX_ERR_MISALIGNED;
+  // q rows are staged with 16-byte bulk copies: every row must start on a 16-byte boundary.
+  if ((a->q_seq_stride & 7) || (a->q_head_stride & 7)) return MUX_ERR_MISALIGNED;
   if (a->bt_seq_stride < 0 || a->bt_head_stride < 0) return MUX_ERR_BAD_SHAPE;
   return MUX_OK;
 }
@@ -525,7 +532,7 @@ static int validate(const mux_attn_mixed_args_t* a) {
     return MUX_ERR_NULL_POINTER;
   if (!aligned16(a->key_cache) || !aligned16(a->value_cache) || !aligned16(a->q) || !aligned16(a->out))
     return MUX_ERR_MISALIGNED;
-  if (a->q_row_stride & 1) return MUX_ERR_MISALIGNED;
+  if (a->q_row_stride & 7) return MUX_ERR_MISALIGNED;
   if (a->bt_item_stride < 0) return MUX_ERR_BAD_SHAPE;
   return MUX_OK;
 }
@@ -538,6 +545,16 @@ static Plan plan_of(const mux_attn_args_t* a) {
 static Plan plan_of(const mux_attn_mixed_args_t* a) {
   return make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len, a->partition_size,
                    a->num_stages, a->flags);
+}
+
+// The scheduling words must be zero at launch.  A caller that keeps its workspace to these
+// calls (zeroed once, never written by anything else) says so with MUX_ATTN_WORKSPACE_CLEAN;
+// otherwise they are cleared here, on the stream, before the launch.
+static int prepare_sched(const Plan& pl, long long items, void* workspace, int flags, cudaStream_t stream) {
+  if (!pl.persistent || (flags & MUX_ATTN_WORKSPACE_CLEAN)) return MUX_OK;
+  const size_t words = 2 + (size_t)items * pl.head_tiles;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, words * 4, stream);
+  return e == cudaSuccess ? MUX_OK : record_cuda_error(e);
 }
 
 static int check_workspace(const Plan& pl, const void* workspace, size_t workspace_bytes) {
@@ -596,6 +613,7 @@ int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t worksp
   prm.nst = pl.nst;
   prm.num_items = (int)items;
   mux::bind_workspace(prm, pl, workspace);
+  if ((st = mux::prepare_sched(pl, items, workspace, a->flags, static_cast<cudaStream_t>(cuda_stream))) != MUX_OK) return st;
   return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
                             static_cast<cudaStream_t>(cuda_stream));
 }
@@ -639,6 +657,7 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
   prm.nst = pl.nst;
   prm.num_items = a->num_items;
   mux::bind_workspace(prm, pl, workspace);
+  if ((st = mux::prepare_sched(pl, a->num_items, workspace, a->flags, static_cast<cudaStream_t>(cuda_stream))) != MUX_OK) return st;
   return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
                            static_cast<cudaStream_t>(cuda_stream));
 }
@@ -694,8 +713,10 @@ extern "C" int mux_paged_attention_static_scratch(const mux_attn_args_t* a, void
   void* scratch = nullptr;
   st = mux::static_scratch_address(&scratch);
   if (st != MUX_OK) return st;
-  // Nothing in the scratch has to be cleared by the caller: scheduling words
-  // carry a per-launch tag and are put back to zero by the kernel itself, and
-  // every partial that is read was written earlier in the same launch.
-  return mux_paged_attention(a, scratch, mux::kStaticScratchBytes, cuda_stream);
+  // Nothing in the scratch has to be cleared by the caller: the array starts
+  // zero-filled, the kernel puts its scheduling words back to zero before it
+  // ends, and every partial that is read was written earlier in the same launch.
+  mux_attn_args_t b = *a;
+  b.flags |= MUX_ATTN_WORKSPACE_CLEAN;
+  return mux_paged_attention(&b, scratch, mux::kStaticScratchBytes, cuda_stream);
 }

@@ -78,13 +78,15 @@ def _stream() -> int:
 
 
 def _workspace(nbytes: int, device: torch.device) -> Optional[torch.Tensor]:
-    """Scratch for partitioned (flash-decoding) launches, cached per (device, stream)."""
+    """Scratch of the attention launches (scheduling words + flash-decoding partials), cached per
+    (device, stream).  It is zero-filled when created and only these ops touch it, which is what
+    MUX_ATTN_WORKSPACE_CLEAN promises to the library."""
     if nbytes == 0:
         return None
     key = (device.index, _stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -187,14 +189,14 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(),
         scale=float(scale), num_seqs=S, num_q_heads=Hq, num_kv_heads=H, head_size=HEAD_SIZE,
         block_size=block_size, max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages, flags=flags)
+        partition_size=partition_size, num_stages=num_stages, flags=flags | _lib.MUX_ATTN_WORKSPACE_CLEAN)
     L = lib()
     need = L.mux_paged_attention_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
     check(L.mux_paged_attention(C.byref(args), ws.data_ptr() if ws is not None else None,
                                 ws.numel() if ws is not None else 0, _stream()), "paged_attention")
     global launch_count
-    launch_count += 0 if S == 0 else (2 if (flags & _lib.MUX_ATTN_GRID_PER_UNIT) and max_context_len > (partition_size or 512) else 1)
+    launch_count += 0 if S == 0 else (2 if not (flags & _lib.MUX_ATTN_PERSISTENT) and max_context_len > (partition_size or 512) else 1)
 
 
 def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
@@ -238,7 +240,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
         item_group=item_group.data_ptr(), item_scale=item_scale.data_ptr(),
         num_items=n, max_group=max_group, head_size=HEAD_SIZE, block_size=block_size,
         max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages, flags=flags)
+        partition_size=partition_size, num_stages=num_stages, flags=flags | _lib.MUX_ATTN_WORKSPACE_CLEAN)
     L = lib()
     need = L.mux_paged_attention_mixed_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
@@ -246,9 +248,15 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                                       ws.numel() if ws is not None else 0, _stream()),
           "paged_attention_mixed")
     global launch_count
-    launch_count += 0 if n == 0 else (2 if (flags & _lib.MUX_ATTN_GRID_PER_UNIT) and max_context_len > (partition_size or 512) else 1)
+    launch_count += 0 if n == 0 else (2 if not (flags & _lib.MUX_ATTN_PERSISTENT) and max_context_len > (partition_size or 512) else 1)
 
 
 def device_status() -> int:
-    """Reads and clears the MUX_DEV_* status bits of the current device (synchronises the stream)."""
-    return check(lib().mux_device_status(_stream()), "device_status")
+    """Reads and clears the MUX_DEV_* status bits of the current device (synchronises the stream).
+    After a non-zero status the cached workspaces are zero-filled again (a launch that gave up
+    on a wait may have left its scheduling words behind)."""
+    st = check(lib().mux_device_status(_stream()), "device_status")
+    if st:
+        for ws in _workspaces.values():
+            ws.zero_()
+    return st

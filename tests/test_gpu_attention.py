@@ -27,7 +27,7 @@ def run(ops, gu, case, kc, vc, head_mapping=None, **kw):
     return out
 
 
-@pytest.mark.parametrize("flags", [0, 1], ids=["persistent", "grid_per_unit"])
+@pytest.mark.parametrize("flags", [0, 1], ids=["grid_per_unit", "persistent"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B", [16, 8, 32])
 @pytest.mark.parametrize("group", [1, 8])
@@ -43,7 +43,7 @@ def test_attention_ragged(env, dtype, B, group, flags):
     assert ops.device_status() == 0
 
 
-@pytest.mark.parametrize("flags", [0, 1], ids=["persistent", "grid_per_unit"])
+@pytest.mark.parametrize("flags", [0, 1], ids=["grid_per_unit", "persistent"])
 @pytest.mark.parametrize("psize,stages", [(16, 4), (64, 4), (128, 8), (512, 8), (1024, 12), (4096, 16)])
 def test_attention_partition_sizes(env, psize, stages, flags):
     """Every partitioning gives the same answer (single partition up to 63 partitions per sequence)."""
@@ -175,8 +175,39 @@ def test_attention_many_units_per_cta_and_repeated_launches(env):
     case, kc, vc = gu.make_case(len(ctx), 8, 8, ctx, 16, torch.float16, seed=77, num_blocks=40000)
     _, _, ref = gu.oracle_step(case, kc, vc)
     for rep in range(3):
-        out = run(ops, gu, case, kc, vc, partition_size=32)          # ~ 10k units on ~ 900 CTAs
+        out = run(ops, gu, case, kc, vc, partition_size=32, flags=1)  # persistent: ~ 10k units on ~ 900 CTAs
         gu.assert_close(out, ref, f"repeat {rep}")
+    assert ops.device_status() == 0
+
+
+def test_attention_dirty_workspace_through_c_abi(env, built_lib):
+    """Straight through the C ABI with a caller workspace full of garbage and no CLEAN flag:
+    the library clears the scheduling words itself."""
+    import ctypes as C
+    ops, gu = env
+    from muxserve_b200 import _lib
+    ctx = [700, 33, 300, 1]
+    case, kc, vc = gu.make_case(len(ctx), 8, 2, ctx, 16, torch.float16, seed=15, num_blocks=512)
+    ops.reshape_and_cache(case.k[0], case.v[0], kc, vc, case.slot_mapping[:, 0, :])
+    q, bt = case.q[0], case.block_tables[0]
+    out = torch.full_like(q, float("nan"))
+    a = _lib.AttnArgs(
+        out=out.data_ptr(), q=q.data_ptr(), q_seq_stride=q.stride(0), q_head_stride=q.stride(1),
+        out_seq_stride=out.stride(0), out_head_stride=out.stride(1), key_cache=kc.data_ptr(),
+        value_cache=vc.data_ptr(), num_blocks=kc.shape[0], head_mapping=None, block_tables=bt.data_ptr(),
+        bt_seq_stride=bt.stride(0), bt_head_stride=bt.stride(1), context_lens=case.context_lens.data_ptr(),
+        scale=case.scale, num_seqs=len(ctx), num_q_heads=8, num_kv_heads=2, head_size=128, block_size=16,
+        max_context_len=case.max_context_len, dtype=_lib.MUX_DTYPE_F16, partition_size=64, num_stages=0,
+        flags=_lib.MUX_ATTN_PERSISTENT)
+    need = built_lib.mux_paged_attention_workspace_size(C.byref(a))
+    ws = torch.full((need,), 0xA5, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        assert built_lib.mux_paged_attention(C.byref(a), ws.data_ptr(), need, stream) == 0
+    torch.cuda.synchronize()
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(out, ref, "dirty workspace")
+    assert int(ws[:8].view(torch.int32).abs().sum()) == 0          # queue and exit words are back to zero
     assert ops.device_status() == 0
 
 
