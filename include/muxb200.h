@@ -216,6 +216,43 @@ size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* arg
 int mux_paged_attention_mixed(const mux_attn_mixed_args_t* args, void* workspace,
                               size_t workspace_bytes, void* cuda_stream);
 
+/* ------------------------------------------------------------------------
+ * decode step — reshape_and_cache and paged_attention of one layer in ONE launch.
+ *
+ * What PagedAttentionWithRoPE does back to back at muxserve/flexserver/models/llama.py:160-161
+ * for a decode batch (one new token per sequence): the new K/V row of every
+ * (sequence, kv head) is appended at position context_len - 1 of that pair's
+ * block list, i.e. slot block_table[(ctx-1)/block_size]*block_size + (ctx-1)%block_size,
+ * the slot csrc/batch_scheduler.h:58-67 puts in slot_mapping, and attention runs over
+ * all context_len tokens.  Same results as mux_reshape_and_cache followed by
+ * mux_paged_attention, bit for bit.  Not available with MUX_ATTN_PERSISTENT.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  mux_attn_args_t attn;
+  const void* k;            /* [num_seqs, num_kv_heads, head_size] new rows (strided views allowed) */
+  const void* v;
+  int64_t k_seq_stride;     /* elements */
+  int64_t k_head_stride;
+  int64_t v_seq_stride;
+  int64_t v_head_stride;
+} mux_decode_args_t;
+
+/* workspace: mux_paged_attention_workspace_size(&args->attn) */
+int mux_decode_attention(const mux_decode_args_t* args, void* workspace, size_t workspace_bytes,
+                         void* cuda_stream);
+
+typedef struct {
+  mux_attn_mixed_args_t attn;
+  const void* k;            /* [num_items, head_size]: one new row per item */
+  const void* v;
+  int64_t k_row_stride;     /* elements */
+  int64_t v_row_stride;
+} mux_decode_mixed_args_t;
+
+/* workspace: mux_paged_attention_mixed_workspace_size(&args->attn) */
+int mux_decode_attention_mixed(const mux_decode_mixed_args_t* args, void* workspace,
+                               size_t workspace_bytes, void* cuda_stream);
+
 /* Reads and clears the device status word (MUX_DEV_* bits) of the current
  * device.  Synchronises the given stream. Returns a negative mux_status_t on failure. */
 int mux_device_status(void* cuda_stream);

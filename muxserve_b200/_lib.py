@@ -75,6 +75,21 @@ class AttnMixedArgs(C.Structure):
     ]
 
 
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("attn", AttnArgs), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("k_seq_stride", C.c_int64), ("k_head_stride", C.c_int64),
+        ("v_seq_stride", C.c_int64), ("v_head_stride", C.c_int64),
+    ]
+
+
+class DecodeMixedArgs(C.Structure):
+    _fields_ = [
+        ("attn", AttnMixedArgs), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("k_row_stride", C.c_int64), ("v_row_stride", C.c_int64),
+    ]
+
+
 _I32P = C.POINTER(C.c_int32)
 _I64P = C.POINTER(C.c_int64)
 
@@ -89,6 +104,8 @@ SIGNATURES = {
     "mux_paged_attention_static_scratch": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "mux_paged_attention_mixed_workspace_size": (C.c_size_t, [C.POINTER(AttnMixedArgs)]),
     "mux_paged_attention_mixed": (C.c_int, [C.POINTER(AttnMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mux_decode_attention": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mux_decode_attention_mixed": (C.c_int, [C.POINTER(DecodeMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),
     "mux_kv_storage_create": (C.c_void_p, [C.c_int32]),
     "mux_kv_storage_destroy": (None, [C.c_void_p]),

@@ -43,6 +43,10 @@ struct AttnParams {
   int max_parts;
   int max_context_len;
   int nst;         // ring depth in tiles
+  // fused cache write (decode step): the new token's K/V rows, one per (sequence, kv head)
+  const void* k_new;
+  const void* v_new;
+  long long kn_s0, kn_s1, vn_s0, vn_s1;  // single model: seq, head strides; mixed: s0 = item (row) stride
   // persistent kernel only
   unsigned* sched;            // [0] unit queue, [1] exit count, [2 + item*head_tiles + tile] merge tickets
   int num_items;

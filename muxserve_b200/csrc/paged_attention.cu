@@ -28,7 +28,10 @@
 
 namespace mux {
 
-template <typename T, int BS, bool MIXED>
+// FUSE: the call is a whole decode step.  The CTA that owns the last partition of an item
+// also appends the item's new token: it patches the staged copy of the last K and V block in
+// shared memory with the new rows (so the attention sees them) and writes them to the pool.
+template <typename T, int BS, bool MIXED, bool FUSE>
 __global__ void __launch_bounds__(kThreads)
 paged_attn_kernel(const __grid_constant__ AttnParams p) {
   constexpr int TILE = kHeadSize * BS * 2;       // bytes of one K or V block
@@ -88,7 +91,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       int id = d.bt_row[part * p.pb + i];
       if (id < 0 || id >= p.num_blocks) {
         atomicOr(p.status, MUX_DEV_BAD_BLOCK_ID);
-        id = 0;
+        id = -1;  // block 0 is read in its place; nothing is ever written through it
       }
       ids[i] = id;
     }
@@ -101,8 +104,8 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
         const int stage = j % nst, use = j / nst;
         if (use > 0)
           mbar_wait(bars + 8 * (kMaxStages + stage), (use - 1) & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
-        const unsigned char* src = j < nblk ? kc + (long long)ids[j] * TILE
-                                            : vc + (long long)ids[j - nblk] * TILE;
+        const long long bid = max(ids[j < nblk ? j : j - nblk], 0);
+        const unsigned char* src = (j < nblk ? kc : vc) + bid * TILE;
         mbar_arrive_expect_tx(bars + 8 * stage, TILE);
         bulk_g2s(ring + stage * TILE, src, TILE, bars + 8 * stage);
       }
@@ -115,6 +118,20 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   float* S = reinterpret_cast<float*>(smem + L.s);
   T* Pm = reinterpret_cast<T*>(smem + L.pm);
   const int SROW = L.srow, PROW = L.prow;
+
+  // FUSE: the warp that will consume the block holding the new token fetches the new rows now.
+  const int new_local = d.ctx - 1 - tok0;  // the appended token's index inside this partition
+  const int jl = new_local / BS, ol = new_local % BS;
+  const bool appends = FUSE && part == nparts - 1 && (jl & (kConsumerWarps - 1)) == warp;
+  const int* ids_c = reinterpret_cast<const int*>(smem + L.ids);
+  uint4 knew = make_uint4(0u, 0u, 0u, 0u);
+  uint2 vnew = make_uint2(0u, 0u);
+  if (appends) {
+    const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
+    const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
+    if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
+    vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
+  }
 
   // q as the B operand (k = d, n = head): b0 = q[g][16ks + 2tq, +1], b1 = q[g][16ks + 8 + 2tq, +1]
   uint32_t qf[8][2];
@@ -142,6 +159,18 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       const int stage = jb % nst, use = jb / nst;
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       const uint32_t tile = ring + stage * TILE;
+      if (FUSE && appends && jb == jl) {  // K row of the new token: 16 pieces of 16 bytes
+        if (lane < 16) {
+          const uint32_t off = lane * CHUNK + ol * 16;
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile + off), "r"(knew.x), "r"(knew.y),
+                       "r"(knew.z), "r"(knew.w) : "memory");
+          if (ids_c[jl] >= 0)
+            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(const_cast<void*>(p.kc)) +
+                                      (long long)ids_c[jl] * TILE + off) = knew;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -203,6 +232,20 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       const int stage = j % nst, use = j / nst;
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       const uint32_t tile = ring + stage * TILE;
+      if (FUSE && appends && jb == jl) {  // V column of the new token: 128 single elements
+        const unsigned short e[4] = {(unsigned short)(vnew.x & 0xffffu), (unsigned short)(vnew.x >> 16),
+                                     (unsigned short)(vnew.y & 0xffffu), (unsigned short)(vnew.y >> 16)};
+        unsigned short* gdst = reinterpret_cast<unsigned short*>(
+            static_cast<unsigned char*>(const_cast<void*>(p.vc)) + (long long)max(ids_c[jl], 0) * TILE);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t off = (4 * lane + i) * VROW + ol * 2;
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(tile + off), "h"(e[i]) : "memory");
+          if (ids_c[jl] >= 0) gdst[off >> 1] = e[i];
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
       const int rem = ntok - jb * BS;  // valid tokens of this block
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -398,7 +441,7 @@ static int ensure_smem(K kern, int smem, int dev, int* granted) {
   return MUX_OK;
 }
 
-template <typename T, int BS, bool MIXED>
+template <typename T, int BS, bool MIXED, bool FUSE>
 static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream) {
   int dev = 0;
   DeviceInfo di;
@@ -406,7 +449,7 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
   if (st != MUX_OK) return st;
   cudaError_t e;
   if (!pl.persistent) {
-    auto kern = paged_attn_kernel<T, BS, MIXED>;
+    auto kern = paged_attn_kernel<T, BS, MIXED, FUSE>;
     static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
     if ((st = ensure_smem(kern, pl.smem, dev, granted)) != MUX_OK) return st;
     cudaLaunchAttribute pdl[1];
@@ -436,6 +479,7 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
     }
     return MUX_OK;
   }
+  if (FUSE) return MUX_ERR_BAD_SHAPE;  // the fused decode step exists for the default scheme only
   auto kern = paged_attn_persistent_kernel<T, BS, MIXED>;
   static int granted[kMaxDevicesTracked] = {};
   static int occ_smem[kMaxDevicesTracked] = {};
@@ -468,7 +512,10 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
 template <bool MIXED>
 static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, int block_size,
                   cudaStream_t stream) {
-#define MUX_CASE(T, BS) return launch_typed<T, BS, MIXED>(prm, pl, items, stream)
+  const bool fuse = prm.k_new != nullptr;
+#define MUX_CASE(T, BS)                                                        \
+  return fuse ? launch_typed<T, BS, MIXED, true>(prm, pl, items, stream)       \
+              : launch_typed<T, BS, MIXED, false>(prm, pl, items, stream)
   if (dtype == MUX_DTYPE_F16) {
     if (block_size == 8) MUX_CASE(__half, 8);
     if (block_size == 16) MUX_CASE(__half, 16);
@@ -573,10 +620,30 @@ size_t mux_paged_attention_workspace_size(const mux_attn_args_t* a) {
   return mux::plan_of(a).total();
 }
 
-int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t workspace_bytes,
-                        void* cuda_stream) {
+}  // extern "C"
+
+namespace mux {
+
+struct NewRows {  // the decode step's new K/V rows; k == nullptr: plain attention
+  const void* k = nullptr;
+  const void* v = nullptr;
+  long long k_s0 = 0, k_s1 = 0, v_s0 = 0, v_s1 = 0;
+};
+
+static int validate_new_rows(const NewRows& n, int flags) {
+  if (n.k == nullptr && n.v == nullptr) return MUX_OK;
+  if (n.k == nullptr || n.v == nullptr) return MUX_ERR_NULL_POINTER;
+  if (flags & MUX_ATTN_PERSISTENT) return MUX_ERR_BAD_SHAPE;
+  if (!aligned16(n.k) || !aligned16(n.v)) return MUX_ERR_MISALIGNED;
+  if ((n.k_s0 & 7) || (n.k_s1 & 7) || (n.v_s0 & 7) || (n.v_s1 & 7)) return MUX_ERR_MISALIGNED;
+  return MUX_OK;
+}
+
+static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* workspace,
+                      size_t workspace_bytes, void* cuda_stream) {
   int st = mux::validate(a);
   if (st != MUX_OK) return st;
+  if ((st = validate_new_rows(rows, a->flags)) != MUX_OK) return st;
   if (a->num_seqs == 0) return MUX_OK;
   const long long items = (long long)a->num_seqs * a->num_kv_heads;
   const mux::Plan pl = mux::plan_of(a);
@@ -612,10 +679,39 @@ int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t worksp
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
   prm.num_items = (int)items;
+  prm.k_new = rows.k;
+  prm.v_new = rows.v;
+  prm.kn_s0 = rows.k_s0;
+  prm.kn_s1 = rows.k_s1;
+  prm.vn_s0 = rows.v_s0;
+  prm.vn_s1 = rows.v_s1;
   mux::bind_workspace(prm, pl, workspace);
   if ((st = mux::prepare_sched(pl, items, workspace, a->flags, static_cast<cudaStream_t>(cuda_stream))) != MUX_OK) return st;
   return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
                             static_cast<cudaStream_t>(cuda_stream));
+}
+
+}  // namespace mux
+
+extern "C" {
+
+int mux_paged_attention(const mux_attn_args_t* a, void* workspace, size_t workspace_bytes,
+                        void* cuda_stream) {
+  return mux::run_single(a, mux::NewRows(), workspace, workspace_bytes, cuda_stream);
+}
+
+int mux_decode_attention(const mux_decode_args_t* a, void* workspace, size_t workspace_bytes,
+                         void* cuda_stream) {
+  if (a == nullptr) return MUX_ERR_NULL_POINTER;
+  if (a->attn.num_seqs > 0 && (a->k == nullptr || a->v == nullptr)) return MUX_ERR_NULL_POINTER;
+  mux::NewRows rows;
+  rows.k = a->k;
+  rows.v = a->v;
+  rows.k_s0 = a->k_seq_stride;
+  rows.k_s1 = a->k_head_stride;
+  rows.v_s0 = a->v_seq_stride;
+  rows.v_s1 = a->v_head_stride;
+  return mux::run_single(&a->attn, rows, workspace, workspace_bytes, cuda_stream);
 }
 
 size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* a) {
@@ -623,10 +719,15 @@ size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* a) 
   return mux::plan_of(a).total();
 }
 
-int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
-                              size_t workspace_bytes, void* cuda_stream) {
+}  // extern "C"
+
+namespace mux {
+
+static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* workspace,
+                     size_t workspace_bytes, void* cuda_stream) {
   int st = mux::validate(a);
   if (st != MUX_OK) return st;
+  if ((st = validate_new_rows(rows, a->flags)) != MUX_OK) return st;
   if (a->num_items == 0) return MUX_OK;
   const mux::Plan pl = mux::plan_of(a);
   if ((st = mux::plan_limits(pl, a->num_items)) != MUX_OK) return st;
@@ -656,10 +757,35 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
   prm.num_items = a->num_items;
+  prm.k_new = rows.k;
+  prm.v_new = rows.v;
+  prm.kn_s0 = rows.k_s0;
+  prm.vn_s0 = rows.v_s0;
   mux::bind_workspace(prm, pl, workspace);
   if ((st = mux::prepare_sched(pl, a->num_items, workspace, a->flags, static_cast<cudaStream_t>(cuda_stream))) != MUX_OK) return st;
   return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
                            static_cast<cudaStream_t>(cuda_stream));
+}
+
+}  // namespace mux
+
+extern "C" {
+
+int mux_paged_attention_mixed(const mux_attn_mixed_args_t* a, void* workspace,
+                              size_t workspace_bytes, void* cuda_stream) {
+  return mux::run_mixed(a, mux::NewRows(), workspace, workspace_bytes, cuda_stream);
+}
+
+int mux_decode_attention_mixed(const mux_decode_mixed_args_t* a, void* workspace,
+                               size_t workspace_bytes, void* cuda_stream) {
+  if (a == nullptr) return MUX_ERR_NULL_POINTER;
+  if (a->attn.num_items > 0 && (a->k == nullptr || a->v == nullptr)) return MUX_ERR_NULL_POINTER;
+  mux::NewRows rows;
+  rows.k = a->k;
+  rows.v = a->v;
+  rows.k_s0 = a->k_row_stride;
+  rows.v_s0 = a->v_row_stride;
+  return mux::run_mixed(&a->attn, rows, workspace, workspace_bytes, cuda_stream);
 }
 
 }  // extern "C"

@@ -132,7 +132,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                     value_cache: torch.Tensor, head_mapping: Optional[torch.Tensor], scale: float,
                     block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
                     max_context_len: int, *, num_kv_heads: Optional[int] = None,
-                    partition_size: int = 0, num_stages: int = 0, flags: int = 0) -> None:
+                    partition_size: int = 0, num_stages: int = 0, flags: int = 0,
+                    _new_kv=None) -> None:
     """Decode attention of one query token per sequence over the paged pool.
 
     ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
@@ -193,10 +194,39 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
     L = lib()
     need = L.mux_paged_attention_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
-    check(L.mux_paged_attention(C.byref(args), ws.data_ptr() if ws is not None else None,
-                                ws.numel() if ws is not None else 0, _stream()), "paged_attention")
+    if _new_kv is None:
+        check(L.mux_paged_attention(C.byref(args), ws.data_ptr() if ws is not None else None,
+                                    ws.numel() if ws is not None else 0, _stream()), "paged_attention")
+    else:
+        k, v = _new_kv
+        _require_cuda(k=k, v=v)
+        Tk, Hk, k_ss, k_hs = _rows(k, "k")
+        Tv, Hv, v_ss, v_hs = _rows(v, "v")
+        if (Tk, Hk) != (S, H) or (Tv, Hv) != (S, H):
+            raise ValueError(f"k and v must hold one new row per (sequence, kv head): [{S}, {H}, {HEAD_SIZE}]")
+        if k.dtype != key_cache.dtype or v.dtype != key_cache.dtype:
+            raise TypeError("k/v dtype differs from the pool dtype")
+        dargs = _lib.DecodeArgs(attn=args, k=k.data_ptr(), v=v.data_ptr(), k_seq_stride=k_ss, k_head_stride=k_hs,
+                                v_seq_stride=v_ss, v_head_stride=v_hs)
+        check(L.mux_decode_attention(C.byref(dargs), ws.data_ptr() if ws is not None else None,
+                                     ws.numel() if ws is not None else 0, _stream()), "decode_attention")
     global launch_count
     launch_count += 0 if S == 0 else (2 if not (flags & _lib.MUX_ATTN_PERSISTENT) and max_context_len > (partition_size or 512) else 1)
+
+
+def decode_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                     key_cache: torch.Tensor, value_cache: torch.Tensor, head_mapping: Optional[torch.Tensor],
+                     scale: float, block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
+                     max_context_len: int, **kw) -> None:
+    """``reshape_and_cache`` + ``paged_attention`` of one layer's decode step in one launch.
+
+    ``k``, ``v``: [S, H*128] or [S, H, 128], the new token of every sequence.  Row (s, h) is
+    appended at position ``context_lens[s] - 1`` of block list ``block_tables[s, h]`` — the slot
+    the reference's ``slot_mapping`` names for a decode step (csrc/batch_scheduler.h:58-67) — and
+    attention runs over all ``context_lens[s]`` tokens.  Results equal the two separate ops bit for bit.
+    """
+    paged_attention(out, q, key_cache, value_cache, head_mapping, scale, block_tables, context_lens,
+                    block_size, max_context_len, _new_kv=(k, v), **kw)
 
 
 def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
@@ -204,14 +234,17 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                           item_context_len: torch.Tensor, item_q_row: torch.Tensor,
                           item_group: torch.Tensor, item_scale: torch.Tensor, block_size: int,
                           max_context_len: int, max_group: int, *, partition_size: int = 0,
-                          num_stages: int = 0, flags: int = 0) -> None:
+                          num_stages: int = 0, flags: int = 0, new_k: Optional[torch.Tensor] = None,
+                          new_v: Optional[torch.Tensor] = None) -> None:
     """One launch for the decode batches of several models sharing the pool.
 
     Item ``i`` is one (sequence, kv head) of some model: q rows
     ``item_q_row[i] .. + item_group[i]`` of the packed ``q``/``out`` [rows, 128]
     attend over block list ``block_tables[i]`` with ``item_context_len[i]`` tokens
     and softmax scale ``item_scale[i]``.  ``muxserve_b200.mixed`` builds these
-    arrays from per-model batches.
+    arrays from per-model batches.  With ``new_k`` / ``new_v`` ([items, 128], one new row per
+    item) the call is the whole decode step: every row is first appended at position
+    ``item_context_len[i] - 1`` of its block list, as ``decode_attention`` does.
     """
     _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, block_tables=block_tables,
                   item_context_len=item_context_len, item_q_row=item_q_row, item_group=item_group,
@@ -244,9 +277,20 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
     L = lib()
     need = L.mux_paged_attention_mixed_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
-    check(L.mux_paged_attention_mixed(C.byref(args), ws.data_ptr() if ws is not None else None,
-                                      ws.numel() if ws is not None else 0, _stream()),
-          "paged_attention_mixed")
+    if new_k is None and new_v is None:
+        check(L.mux_paged_attention_mixed(C.byref(args), ws.data_ptr() if ws is not None else None,
+                                          ws.numel() if ws is not None else 0, _stream()),
+              "paged_attention_mixed")
+    else:
+        _require_cuda(new_k=new_k, new_v=new_v)
+        for name, t in (("new_k", new_k), ("new_v", new_v)):
+            if t.dim() != 2 or tuple(t.shape) != (n, HEAD_SIZE) or t.stride(1) != 1 or t.dtype != q.dtype:
+                raise ValueError(f"{name} must be [{n}, {HEAD_SIZE}] of the pool dtype with a dense last dim")
+        dargs = _lib.DecodeMixedArgs(attn=args, k=new_k.data_ptr(), v=new_v.data_ptr(),
+                                     k_row_stride=new_k.stride(0), v_row_stride=new_v.stride(0))
+        check(L.mux_decode_attention_mixed(C.byref(dargs), ws.data_ptr() if ws is not None else None,
+                                           ws.numel() if ws is not None else 0, _stream()),
+              "decode_attention_mixed")
     global launch_count
     launch_count += 0 if n == 0 else (2 if not (flags & _lib.MUX_ATTN_PERSISTENT) and max_context_len > (partition_size or 512) else 1)
 

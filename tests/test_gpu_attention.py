@@ -180,6 +180,32 @@ def test_attention_many_units_per_cta_and_repeated_launches(env):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("dtype,B,group,psize", [(torch.float16, 16, 1, 0), (torch.bfloat16, 16, 8, 128),
+                                                 (torch.float16, 8, 2, 64), (torch.bfloat16, 32, 12, 0)])
+def test_fused_decode_step_equals_two_ops(env, dtype, B, group, psize):
+    """decode_attention == reshape_and_cache then paged_attention: pool and output, bit for bit."""
+    ops, gu = env
+    ctx = [1, 2, B, B + 1, 2 * B, 255, 256, 257, 513, 1000, 77, 16, 17, 512]
+    H = 3
+    case, kc, vc = gu.make_case(len(ctx), H * group, H, ctx, B, dtype, seed=50 + B, num_blocks=2048)
+    kc2, vc2 = kc.clone(), vc.clone()
+    expect = run(ops, gu, case, kc, vc, partition_size=psize)
+    # k, v as strided views of a fused qkv buffer
+    S = len(ctx)
+    kv = torch.zeros(S, 2 * H * 128, dtype=dtype, device="cuda")
+    kv[:, :H * 128] = case.k[0].reshape(S, -1)
+    kv[:, H * 128:] = case.v[0].reshape(S, -1)
+    got = torch.full_like(expect, float("nan"))
+    ops.decode_attention(got, case.q[0], kv[:, :H * 128], kv[:, H * 128:], kc2, vc2, None, case.scale,
+                         case.block_tables[0], case.context_lens, B, case.max_context_len, partition_size=psize)
+    assert torch.equal(kc2.view(torch.int16), kc.view(torch.int16))
+    assert torch.equal(vc2.view(torch.int16), vc.view(torch.int16))
+    assert torch.equal(got, expect)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(got, ref, "fused decode step")
+    assert ops.device_status() == 0
+
+
 def test_attention_dirty_workspace_through_c_abi(env, built_lib):
     """Straight through the C ABI with a caller workspace full of garbage and no CLEAN flag:
     the library clears the scheduling words itself."""

@@ -39,3 +39,39 @@ def test_mixed_launch_matches_per_model_and_oracle(built_lib, dtype, psize):
                                       b.context_lens, 16)
             gu.assert_close(got, ref, f"{b.name} layer {layer}")
     assert ops.device_status() == 0
+
+
+def test_mixed_fused_decode_step(built_lib):
+    """The mixed launch with new rows appended in the same kernel == per-model cache writes + mixed attention."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from muxserve_b200 import mixed, ops, workloads
+    from test_mixed_plan import make_batches
+    batches, num_blocks, gen = make_batches(device="cuda", seed=21)
+    dtype = torch.float16
+    kc = torch.randn(num_blocks, 16, 16, 8, generator=gen).to(dtype).cuda()
+    vc = torch.randn(num_blocks, 128, 16, generator=gen).to(dtype).cuda()
+    kc2, vc2 = kc.clone(), vc.clone()
+    plan = mixed.build_mixed_plan(batches, "cuda")
+    qs = [torch.randn(b.num_seqs, b.num_q_heads, 128, generator=gen).to(dtype).cuda() for b in batches]
+    ks = [torch.randn(b.num_seqs, b.num_kv_heads, 128, generator=gen).to(dtype).cuda() for b in batches]
+    vs = [torch.randn(b.num_seqs, b.num_kv_heads, 128, generator=gen).to(dtype).cuda() for b in batches]
+    packed = mixed.pack_rows(plan, qs)
+    k_items, v_items = mixed.pack_rows(plan, ks), mixed.pack_rows(plan, vs)
+    layer = 1
+    n_items, n_rows = plan.active(layer)
+    # two-op path
+    for b, k, v in zip(batches, ks, vs):
+        if b.num_layers > layer:
+            slots = workloads.last_token_slots(b.block_tables, b.context_lens, 16)[:, layer, :]
+            ops.reshape_and_cache(k, v, kc, vc, slots)
+    expect = torch.zeros_like(packed)
+    args = (plan.block_tables[layer, :n_items], plan.item_context_len[:n_items], plan.item_q_row[:n_items],
+            plan.item_group[:n_items], plan.item_scale[:n_items], 16, plan.max_context_len, plan.max_group)
+    ops.paged_attention_mixed(expect[:n_rows], packed[:n_rows], kc, vc, *args)
+    got = torch.zeros_like(packed)
+    ops.paged_attention_mixed(got[:n_rows], packed[:n_rows], kc2, vc2, *args, new_k=k_items[:n_items],
+                              new_v=v_items[:n_items])
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc)
+    assert torch.equal(got, expect)
+    assert ops.device_status() == 0
