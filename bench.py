@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--attn-flags", type=int, default=0, help="MUX_ATTN_* bits passed to paged_attention (1 = persistent kernel)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiler captures)")
     ap.add_argument("--seed", type=int, default=20240531)
+    ap.add_argument("--two-op", action="store_true",
+                    help="time reshape_and_cache + paged_attention as separate calls instead of the fused decode step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel leg at N > 1")
@@ -276,19 +278,29 @@ def run_native(args):
     out = torch.empty((S, Hq, 128), dtype=dt, device=dev)
     psize, nst = args.partition_size, args.num_stages
 
-    def layer(l, ev=None):
+    fused = NT == 1 and not args.two_op and not (args.attn_flags & 1)
+
+    def layer(l, ev=None, fuse=fused):
         r = l % L_res
-        ops.reshape_and_cache(case.k[r], case.v[r], kc, vc, case.slot_mapping[:, r, :])
-        if ev is not None:
-            ev[0].record()
-        ops.paged_attention(out, case.q[r], kc, vc, None, case.scale, case.block_tables[r], case.context_lens,
-                            BLOCK, case.max_context_len, partition_size=psize, num_stages=nst, flags=args.attn_flags)
+        if fuse:      # one launch: append the new token and attend
+            if ev is not None:
+                ev[0].record()
+            ops.decode_attention(out, case.q[r], case.k[r], case.v[r], kc, vc, None, case.scale, case.block_tables[r],
+                                 case.context_lens, BLOCK, case.max_context_len, partition_size=psize,
+                                 num_stages=nst, flags=args.attn_flags)
+        else:
+            ops.reshape_and_cache(case.k[r], case.v[r], kc, vc, case.slot_mapping[:, r, :])
+            if ev is not None:
+                ev[0].record()
+            ops.paged_attention(out, case.q[r], kc, vc, None, case.scale, case.block_tables[r], case.context_lens,
+                                BLOCK, case.max_context_len, partition_size=psize, num_stages=nst,
+                                flags=args.attn_flags)
         if ev is not None:
             ev[1].record()
 
-    def step(events=None):
+    def step(events=None, fuse=fused):
         for l in range(L):
-            layer(l, None if events is None else events[l])
+            layer(l, None if events is None else events[l], fuse)
 
     def barrier():
         if world > 1:
@@ -324,6 +336,22 @@ def run_native(args):
     ms_step = ms_total / args.steps
     attn_ms = sum(a.elapsed_time(b) for evs in events for a, b in evs) / (args.steps * L)
     status = ops.device_status() | status_warm
+
+    # ---- the same step with the two reference-signature ops (separate cache-write launch) ----
+    two_op = None
+    if fused:
+        for _ in range(3):
+            step(fuse=False)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step(fuse=False)
+        e1.record()
+        barrier()
+        ms2 = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+        two_op = {"ms_per_step": ms2, "tokens_per_s": world * S / (ms2 * 1e-3),
+                  "whole_path_gbs": (attn_bytes + cw_bytes) * L / (ms2 * 1e-3) / 1e9,
+                  "note": "reshape_and_cache and paged_attention as two calls per layer"}
 
     # ---- end-to-end leg: host buffers, copies inside the timed region ----
     e2e = None
@@ -406,7 +434,8 @@ def run_native(args):
 
     if rank == 0:
         peak, peak_src = hbm_peak()
-        achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+        launch_bytes = attn_bytes + (cw_bytes if fused else 0)
+        achieved = launch_bytes / (attn_ms * 1e-3) / 1e9
         path_gbs = (attn_bytes + cw_bytes) * L / (ms_step * 1e-3) / 1e9
         traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if args.layers == 0 else None
         line = {
@@ -423,12 +452,18 @@ def run_native(args):
                                      f"{world} independent model replicas, one per GPU, no data-path collective"),
                        "partition_size": psize or "library default", "num_stages": nst or "library default"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "kernel": "paged_attn_kernel (+ merge kernel when partitioned)",
-                         "algorithmic_bytes_per_launch": attn_bytes, "avg_launch_ms": attn_ms, "peak_source": peak_src,
-                         "whole_path_gbs": path_gbs},
+                         "traffic": traffic,
+                         "kernel": ("paged_attn_kernel<fused cache write> (+ merge kernel)" if fused else
+                                    "paged_attn_kernel (+ merge kernel)"),
+                         "algorithmic_bytes_per_launch": launch_bytes, "avg_launch_ms": attn_ms,
+                         "peak_source": peak_src, "whole_path_gbs": path_gbs},
+            "step": ("decode_attention per layer (cache write fused into the attention launch)" if fused else
+                     "reshape_and_cache + paged_attention per layer"),
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
             "clocks": clocks, "device_status": status,
         }
+        if two_op is not None:
+            line["two_op"] = two_op
         if tp is not None:
             line["tp"] = tp
         print(json.dumps(line), flush=True)

@@ -7,7 +7,9 @@ muxserve/flexserver/llm_runtime.py:300-327) and synchronises at its end (:274).
 uploads q / k / v and that layer's block tables from pinned host memory on a
 copy stream, runs ``reshape_and_cache`` + ``paged_attention`` on the caller's
 stream and downloads the layer's output on a third stream, so that transfers of
-neighbouring layers overlap the kernels.
+neighbouring layers overlap the kernels.  With one new token per sequence the two ops run
+as the fused ``decode_attention`` launch (``slot_mapping`` is still uploaded, as the reference
+does, but the kernel derives the slots from the block tables).
 """
 from __future__ import annotations
 
@@ -20,12 +22,13 @@ from .workloads import HEAD_SIZE, ModelShape
 class HostDecodeStep:
     def __init__(self, shape: ModelShape, block_size: int, dtype: torch.dtype, key_cache: torch.Tensor,
                  value_cache: torch.Tensor, max_blocks_per_seq: int, new_tokens: int = 1, depth: int = 4,
-                 partition_size: int = 0, num_stages: int = 0):
+                 partition_size: int = 0, num_stages: int = 0, fused: bool = True):
         dev = key_cache.device
         self.shape, self.block_size, self.dtype = shape, block_size, dtype
         self.kc, self.vc = key_cache, value_cache
         self.depth = depth
         self.partition_size, self.num_stages = partition_size, num_stages
+        self.fused = fused and new_tokens == 1   # one launch per layer when one token per sequence is appended
         S, T = shape.batch, shape.batch * new_tokens
         self.q = torch.empty((depth, S, shape.num_q_heads, HEAD_SIZE), dtype=dtype, device=dev)
         self.out = torch.empty_like(self.q)
@@ -70,10 +73,15 @@ class HostDecodeStep:
                 self.ready[b].record(cs)
             h2d += (self.q[b].numel() + 2 * self.k[b].numel()) * self.q.element_size() + self.bt[b].numel() * 4
             compute.wait_event(self.ready[b])
-            ops.reshape_and_cache(self.k[b], self.v[b], self.kc, self.vc, self.slots[:, l, :])
-            ops.paged_attention(self.out[b], self.q[b], self.kc, self.vc, None, HEAD_SIZE ** -0.5, self.bt[b],
-                                self.ctx, self.block_size, max_context_len,
-                                partition_size=self.partition_size, num_stages=self.num_stages)
+            if self.fused:
+                ops.decode_attention(self.out[b], self.q[b], self.k[b], self.v[b], self.kc, self.vc, None,
+                                     HEAD_SIZE ** -0.5, self.bt[b], self.ctx, self.block_size, max_context_len,
+                                     partition_size=self.partition_size, num_stages=self.num_stages)
+            else:
+                ops.reshape_and_cache(self.k[b], self.v[b], self.kc, self.vc, self.slots[:, l, :])
+                ops.paged_attention(self.out[b], self.q[b], self.kc, self.vc, None, HEAD_SIZE ** -0.5, self.bt[b],
+                                    self.ctx, self.block_size, max_context_len,
+                                    partition_size=self.partition_size, num_stages=self.num_stages)
             self.done[b].record(compute)
             os_.wait_event(self.done[b])
             with torch.cuda.stream(os_):
