@@ -63,8 +63,8 @@ def parse_args():
     ap.add_argument("--pool-frac", type=float, default=0.6, help="fraction of HBM given to the KV pool")
     ap.add_argument("--partition-size", type=int, default=0)
     ap.add_argument("--num-stages", type=int, default=0)
-    ap.add_argument("--attn-flags", type=int, default=0, help="MUX_ATTN_* bits passed to paged_attention (1 = persistent kernel)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiler captures)")
+    ap.add_argument("--batch", type=int, default=0, help="override the batch size (small profiler captures)")
     ap.add_argument("--seed", type=int, default=20240531)
     ap.add_argument("--two-op", action="store_true",
                     help="time reshape_and_cache + paged_attention as separate calls instead of the fused decode step")
@@ -256,6 +256,8 @@ def run_native(args):
     w = dict(WORKLOADS[args.workload])
     if args.layers > 0:
         w["L"] = args.layers
+    if args.batch > 0:
+        w["S"] = args.batch
     dt = DTYPES[w["dtype"]]
     L, S, Hq, H, NT = w["L"], w["S"], w["Hq"], w["H"], w["new_tokens"]
 
@@ -278,7 +280,7 @@ def run_native(args):
     out = torch.empty((S, Hq, 128), dtype=dt, device=dev)
     psize, nst = args.partition_size, args.num_stages
 
-    fused = NT == 1 and not args.two_op and not (args.attn_flags & 1)
+    fused = NT == 1 and not args.two_op
 
     def layer(l, ev=None, fuse=fused):
         r = l % L_res
@@ -287,14 +289,13 @@ def run_native(args):
                 ev[0].record()
             ops.decode_attention(out, case.q[r], case.k[r], case.v[r], kc, vc, None, case.scale, case.block_tables[r],
                                  case.context_lens, BLOCK, case.max_context_len, partition_size=psize,
-                                 num_stages=nst, flags=args.attn_flags)
+                                 num_stages=nst)
         else:
             ops.reshape_and_cache(case.k[r], case.v[r], kc, vc, case.slot_mapping[:, r, :])
             if ev is not None:
                 ev[0].record()
             ops.paged_attention(out, case.q[r], kc, vc, None, case.scale, case.block_tables[r], case.context_lens,
-                                BLOCK, case.max_context_len, partition_size=psize, num_stages=nst,
-                                flags=args.attn_flags)
+                                BLOCK, case.max_context_len, partition_size=psize, num_stages=nst)
         if ev is not None:
             ev[1].record()
 
@@ -437,7 +438,7 @@ def run_native(args):
         launch_bytes = attn_bytes + (cw_bytes if fused else 0)
         achieved = launch_bytes / (attn_ms * 1e-3) / 1e9
         path_gbs = (attn_bytes + cw_bytes) * L / (ms_step * 1e-3) / 1e9
-        traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if args.layers == 0 else None
+        traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload) if args.batch == 0 else None
         line = {
             "metric": METRIC, "value": world * S / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,

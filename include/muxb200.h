@@ -42,22 +42,12 @@ typedef enum {
 
 typedef enum { MUX_DTYPE_F16 = 0, MUX_DTYPE_BF16 = 1 } mux_dtype_t;
 
-/* mux_attn_args_t.flags.  Default (0): one CTA per (item, partition) and a small second
- * kernel that merges the partitions.  PERSISTENT: one wave of CTAs pulls work units from a
- * queue and the last partition of an item to finish merges them in the same launch (one
- * launch instead of two; measured slower on large batches). */
-#define MUX_ATTN_PERSISTENT 1
-/* The leading mux_*_workspace_size bytes' scheduling words are known to be zero: the
- * workspace was zero-filled once and has since been used only by these calls (which leave
- * it zero-filled).  Without this flag the words are cleared on the stream before each
- * launch.  After a non-zero mux_device_status treat the workspace as dirty again. */
-#define MUX_ATTN_WORKSPACE_CLEAN 2
-
 /* Bits of the device status word (mux_device_status). */
-#define MUX_DEV_BAD_BLOCK_ID 1u   /* a block id outside [0, num_blocks) was met and replaced by 0 */
+#define MUX_DEV_BAD_BLOCK_ID 1u   /* a block id outside [0, num_blocks) was met; block 0 was read in its place */
 #define MUX_DEV_WAIT_TIMEOUT 2u   /* a bounded wait on a staged copy ran out */
 #define MUX_DEV_BAD_CONTEXT 4u    /* a context length above max_context_len (or < 0) was met */
 #define MUX_DEV_BAD_SLOT 8u       /* a slot outside the pool was met and skipped */
+#define MUX_DEV_BAD_HEAD_MAPPING 16u /* head_mapping does not give every kv head num_q_heads/num_kv_heads q heads */
 
 const char* mux_strerror(int status);
 /* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
@@ -116,11 +106,10 @@ int mux_reshape_and_cache(const mux_cache_write_args_t* args, void* cuda_stream)
  * never read (the reference leaves them uninitialised).
  *
  * Long contexts are split into partitions of partition_size tokens that are
- * combined through the caller's workspace (flash-decoding), which also holds
- * the launch's scheduling words.  Size (never 0 for a non-empty batch) comes
- * from mux_paged_attention_workspace_size; contents need no initialisation
- * (but see MUX_ATTN_WORKSPACE_CLEAN) and two launches that may overlap on the
- * GPU must not share a workspace.
+ * combined through the caller's workspace (flash-decoding).  Sizes come from
+ * mux_paged_attention_workspace_size; workspace may be NULL when that is 0, its
+ * contents need no initialisation, and two launches that may overlap on the GPU
+ * must not share it.
  * ---------------------------------------------------------------------- */
 typedef struct {
   void* out;                   /* [num_seqs, num_q_heads, head_size] */
@@ -147,7 +136,7 @@ typedef struct {
   int32_t dtype;               /* mux_dtype_t */
   int32_t partition_size;      /* tokens, multiple of block_size; 0 = library heuristic */
   int32_t num_stages;          /* depth of the shared-memory block ring (multiple of 4, <= 16); 0 = default */
-  int32_t flags;               /* MUX_ATTN_* bits, normally 0 */
+  int32_t flags;               /* reserved, must be 0 */
   int32_t reserved;
 } mux_attn_args_t;
 
@@ -225,7 +214,7 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* args, void* workspace
  * block list, i.e. slot block_table[(ctx-1)/block_size]*block_size + (ctx-1)%block_size,
  * the slot csrc/batch_scheduler.h:58-67 puts in slot_mapping, and attention runs over
  * all context_len tokens.  Same results as mux_reshape_and_cache followed by
- * mux_paged_attention, bit for bit.  Not available with MUX_ATTN_PERSISTENT.
+ * mux_paged_attention, bit for bit.
  * ---------------------------------------------------------------------- */
 typedef struct {
   mux_attn_args_t attn;

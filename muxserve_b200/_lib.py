@@ -20,9 +20,7 @@ MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 
-ABI_VERSION = 2
-MUX_ATTN_PERSISTENT = 1
-MUX_ATTN_WORKSPACE_CLEAN = 2
+ABI_VERSION = 3
 
 
 class CacheWriteArgs(C.Structure):

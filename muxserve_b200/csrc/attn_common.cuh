@@ -47,24 +47,19 @@ struct AttnParams {
   const void* k_new;
   const void* v_new;
   long long kn_s0, kn_s1, vn_s0, vn_s1;  // single model: seq, head strides; mixed: s0 = item (row) stride
-  // persistent kernel only
-  unsigned* sched;            // [0] unit queue, [1] exit count, [2 + item*head_tiles + tile] merge tickets
-  int num_items;
-  int num_chunks;             // ceil(num_items / 32)
 };
 
 // Shared-memory carve-up, identical on host (sizing) and device.
 struct SmemLayout {
-  int ring, s, pm, ids, info, bars, total;
-  int srow, prow;
+  int ring, s, ids, info, bars, total;
+  int srow;
 };
 
 __host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs, int nst) {
   SmemLayout L;
   const int tile = kHeadSize * block_size * 2;
   const int P = pb * block_size;
-  L.srow = P + 8;
-  L.prow = P + 16;
+  L.srow = P + 16;  // rows 64 bytes apart modulo 128: conflict-free 16-byte reads of the weights
   int off = 0;
   L.ring = off;
   off += nst * tile;
@@ -72,9 +67,6 @@ __host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs
   int s_bytes = gs * L.srow * 4;
   int red_bytes = kConsumerWarps * gs * kRedStride * 4;
   off += (s_bytes > red_bytes ? s_bytes : red_bytes);
-  off = (off + 15) & ~15;
-  L.pm = off;
-  off += 2 * gs * L.prow * 2;  // P as hi + lo planes
   off = (off + 15) & ~15;
   L.ids = off;
   off += pb * 4;

@@ -4,8 +4,6 @@
 
 #include "../../include/muxb200.h"
 
-#define MUX_DEV_BAD_HEAD_MAPPING 16u
-
 namespace mux {
 
 // Device address of the status word of the CURRENT device (one word per device,

@@ -12,8 +12,9 @@
 // bytes are used as they arrive.
 //
 //   phase 1  logits[h][t] = scale * K[t,:] . q[h,:]   for all K blocks of the unit
-//   softmax  over the unit (max, exp, sum) -> P split into hi + lo parts of the KV dtype
-//            (two MMAs per tile; keeps fp32-level accuracy of P with 16-bit operands)
+//   softmax  over the unit (max, exp, sum); the weights stay fp32 in place of the logits
+//            and are split into hi + lo parts of the KV dtype when they are loaded as MMA
+//            operands (two MMAs per tile: fp32-level accuracy of P with 16-bit operands)
 //   phase 2  out^T[d][h] += V^T[d,t] P^T[t,h]         for all V blocks of the unit
 //
 // A unit that covers its whole context writes `out`; otherwise it writes an
@@ -24,7 +25,6 @@
 #include <mutex>
 
 #include "attn_common.cuh"
-#include "attn_persistent.cuh"
 
 namespace mux {
 
@@ -116,8 +116,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   // ---------------- consumer warps ----------------
   const int g = lane >> 2, tq = lane & 3;
   float* S = reinterpret_cast<float*>(smem + L.s);
-  T* Pm = reinterpret_cast<T*>(smem + L.pm);
-  const int SROW = L.srow, PROW = L.prow;
+  const int SROW = L.srow;
 
   // FUSE: the warp that will consume the block holding the new token fetches the new rows now.
   const int new_local = d.ctx - 1 - tok0;  // the appended token's index inside this partition
@@ -203,14 +202,11 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     for (int t = lane; t < ntok; t += 32) m = fmaxf(m, srow[t]);
     m = warp_max(m);
     float l = 0.f;
-    T* prow = Pm + n * PROW;
-    T* prow_lo = prow + p.gs * PROW;
+    float* prow = S + n * SROW;  // exp(logit - max) overwrites the logit
     for (int t = lane; t < nblk * BS; t += 32) {
-      float pv = t < ntok ? __expf(srow[t] - m) : 0.f;
+      const float pv = t < ntok ? __expf(srow[t] - m) : 0.f;
       l += pv;
-      const T hi = from_float<T>(pv);
-      prow[t] = hi;
-      prow_lo[t] = from_float<T>(pv - to_float(hi));
+      prow[t] = pv;
     }
     l = warp_sum(l);
     if (lane == 0) {
@@ -225,7 +221,6 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
   {
-    const uint32_t pm_base = smem_u32(Pm);
     const bool lane_has = (BS >= 16) || (tq < 2);
     for (int jb = warp; jb < nblk; jb += kConsumerWarps) {
       const int j = nblk + jb;
@@ -254,13 +249,9 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
         const int t0 = ks * 16 + 4 * tq;
         uint32_t b0 = 0u, b1 = 0u, c0 = 0u, c1 = 0u;
         if (g < geff && lane_has) {
-          const uint32_t pa = pm_base + (g * PROW + jb * BS + t0) * 2;
-          uint2 pv = lds64(pa);
-          b0 = pv.x;
-          b1 = pv.y;
-          pv = lds64(pa + p.gs * PROW * 2);
-          c0 = pv.x;
-          c1 = pv.y;
+          const float4 pw = *reinterpret_cast<const float4*>(S + g * SROW + jb * BS + t0);
+          split_pair<T>(pw.x, pw.y, b0, c0);
+          split_pair<T>(pw.z, pw.w, b1, c1);
         }
         uint32_t mlo = 0xffffffffu, mhi = 0xffffffffu;
         if (rem < BS) {  // stale tail of the last block may hold anything, NaN included
@@ -283,7 +274,9 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     }
   }
 
-  // ---- cross-warp reduction (aliases the logits, which are dead by now) ----
+  // ---- cross-warp reduction.  It reuses the buffer of the softmax weights, which the other
+  // warps may still be reading: wait for all of them to finish phase 2 first.
+  named_bar_sync(1, kConsumerThreads);
   float* red = S;
   {
     const int n0 = 2 * tq;
@@ -358,24 +351,24 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
 // ------------------------------------------------------------------ host side
 
 struct Plan {
-  bool persistent;
-  int pb, max_parts, gs, head_tiles, nst, smem, num_chunks;
-  size_t sched_bytes, ws_acc_bytes, ws_ml_bytes;
-  size_t total() const { return sched_bytes + ws_acc_bytes + ws_ml_bytes; }
+  int pb, max_parts, gs, head_tiles, nst, smem;
+  size_t ws_acc_bytes, ws_ml_bytes;
+  size_t total() const { return ws_acc_bytes + ws_ml_bytes; }
 };
 
-static int default_stages(int block_size) {
-  // 32 KiB of staged blocks per CTA.
+static int default_stages(int block_size, int gs) {
+  // 32 KiB of staged blocks per CTA; 16 KiB for grouped heads, whose logits and softmax
+  // weights already take tens of KiB (more resident CTAs beat a deeper ring there).
   int tile = kHeadSize * block_size * 2;
-  int n = (32 * 1024) / tile;
+  int n = ((gs > 2 ? 16 : 32) * 1024) / tile;
   return std::max(kConsumerWarps, std::min(kMaxStages, n));
 }
 
 static Plan make_plan(long long items, int group, int block_size, int max_context_len,
                       int partition_size, int num_stages, int flags) {
   Plan pl;
-  pl.persistent = (flags & MUX_ATTN_PERSISTENT) != 0;
-  int psize = partition_size > 0 ? partition_size : (pl.persistent ? 256 : 512);
+  (void)flags;
+  int psize = partition_size > 0 ? partition_size : 512;
   psize = std::max(block_size, (psize / block_size) * block_size);
   pl.pb = psize / block_size;
   pl.max_parts = std::max(1, (max_context_len + psize - 1) / psize);
@@ -384,12 +377,9 @@ static Plan make_plan(long long items, int group, int block_size, int max_contex
   // The ring depth must be a multiple of the consumer-warp count: then every
   // stage is always consumed by the same warp, whose mbarrier parity waits are
   // therefore never more than one phase apart.
-  pl.nst = num_stages > 0 ? num_stages : default_stages(block_size);
+  pl.nst = num_stages > 0 ? num_stages : default_stages(block_size, pl.gs);
   pl.nst = std::min(kMaxStages, std::max(kConsumerWarps, (pl.nst / kConsumerWarps) * kConsumerWarps));
-  pl.num_chunks = (int)((items + 31) / 32);
-  pl.smem = pl.persistent ? psmem_layout(block_size, pl.pb, pl.gs, pl.nst, pl.num_chunks).total
-                          : smem_layout(block_size, pl.pb, pl.gs, pl.nst).total;
-  pl.sched_bytes = kSchedBytes;  // same layout for both launch schemes
+  pl.smem = smem_layout(block_size, pl.pb, pl.gs, pl.nst).total;
   if (pl.max_parts > 1) {
     size_t slots = (size_t)items * pl.head_tiles * pl.max_parts * pl.gs;
     pl.ws_acc_bytes = slots * kHeadSize * sizeof(float);
@@ -402,12 +392,7 @@ static Plan make_plan(long long items, int group, int block_size, int max_contex
 
 static int plan_limits(const Plan& pl, long long items) {
   if (pl.smem > kMaxSmemBytes) return MUX_ERR_BAD_SHAPE;  // partition too large for one SM
-  if (pl.persistent) {
-    if (pl.num_chunks > kMaxChunks || pl.pb > kMaxPB || items * pl.head_tiles > kMaxTickets)
-      return MUX_ERR_TOO_LARGE;
-  } else if (items > 0x7fffffffLL || pl.max_parts > 65535) {
-    return MUX_ERR_BAD_SHAPE;
-  }
+  if (items > 0x7fffffffLL || pl.max_parts > 65535) return MUX_ERR_BAD_SHAPE;
   return MUX_OK;
 }
 
@@ -448,64 +433,33 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
   int st = device_info(&dev, &di);
   if (st != MUX_OK) return st;
   cudaError_t e;
-  if (!pl.persistent) {
-    auto kern = paged_attn_kernel<T, BS, MIXED, FUSE>;
-    static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
-    if ((st = ensure_smem(kern, pl.smem, dev, granted)) != MUX_OK) return st;
-    cudaLaunchAttribute pdl[1];
-    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    pdl[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = (size_t)pl.smem;
-    cfg.stream = stream;
-    cfg.attrs = pdl;
-    cfg.numAttrs = 1;
-    if ((e = cudaLaunchKernelEx(&cfg, kern, prm)) != cudaSuccess) return record_cuda_error(e);
-    if (pl.max_parts > 1) {
-      dim3 mgrid((unsigned)items, (unsigned)pl.head_tiles);
-      static bool carve[kMaxDevicesTracked] = {};
-      if (!carve[dev]) {  // same shared-memory carve-out as the main kernel: no SM reconfiguration between them
-        cudaFuncSetAttribute(paged_attn_merge_kernel<T, BS, MIXED>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
-        carve[dev] = true;
-      }
-      cfg.gridDim = mgrid;
-      cfg.blockDim = dim3(kHeadSize);
-      cfg.dynamicSmemBytes = 0;
-      if ((e = cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel<T, BS, MIXED>, prm)) != cudaSuccess)
-        return record_cuda_error(e);
-    }
-    return MUX_OK;
-  }
-  if (FUSE) return MUX_ERR_BAD_SHAPE;  // the fused decode step exists for the default scheme only
-  auto kern = paged_attn_persistent_kernel<T, BS, MIXED>;
-  static int granted[kMaxDevicesTracked] = {};
-  static int occ_smem[kMaxDevicesTracked] = {};
-  static int occ_val[kMaxDevicesTracked] = {};
+  auto kern = paged_attn_kernel<T, BS, MIXED, FUSE>;
+  static int granted[kMaxDevicesTracked] = {};  // per instantiation, per device
   if ((st = ensure_smem(kern, pl.smem, dev, granted)) != MUX_OK) return st;
-  if (occ_val[dev] == 0 || occ_smem[dev] != pl.smem) {
-    int occ = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kThreads, pl.smem);
-    if (e != cudaSuccess) return record_cuda_error(e);
-    occ_val[dev] = std::max(1, occ);
-    occ_smem[dev] = pl.smem;
-  }
-  const long long upper = items * pl.head_tiles * (long long)pl.max_parts;  // bound on the unit count
-  const unsigned grid = (unsigned)std::max(1LL, std::min<long long>(upper, (long long)di.sms * occ_val[dev]));
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = (size_t)pl.smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
+  cfg.attrs = pdl;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, prm);
-  if (e != cudaSuccess) return record_cuda_error(e);
+  if ((e = cudaLaunchKernelEx(&cfg, kern, prm)) != cudaSuccess) return record_cuda_error(e);
+  if (pl.max_parts > 1) {
+    static bool carve[kMaxDevicesTracked] = {};
+    if (!carve[dev]) {  // same shared-memory carve-out as the main kernel: no SM reconfiguration between them
+      cudaFuncSetAttribute(paged_attn_merge_kernel<T, BS, MIXED>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared);
+      carve[dev] = true;
+    }
+    cfg.gridDim = dim3((unsigned)items, (unsigned)pl.head_tiles);
+    cfg.blockDim = dim3(kHeadSize);
+    cfg.dynamicSmemBytes = 0;
+    if ((e = cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel<T, BS, MIXED>, prm)) != cudaSuccess)
+      return record_cuda_error(e);
+  }
   return MUX_OK;
 }
 
@@ -528,13 +482,11 @@ static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, i
 #undef MUX_CASE
 }
 
-// Splits the caller's workspace into scheduling words and partials.
+// Splits the caller's workspace into the two partial arrays.
 static void bind_workspace(AttnParams& prm, const Plan& pl, void* workspace) {
   char* base = static_cast<char*>(workspace);
-  prm.sched = pl.sched_bytes ? reinterpret_cast<unsigned*>(base) : nullptr;
-  prm.ws_acc = pl.ws_acc_bytes ? reinterpret_cast<float*>(base + pl.sched_bytes) : nullptr;
-  prm.ws_ml = pl.ws_ml_bytes ? reinterpret_cast<float*>(base + pl.sched_bytes + pl.ws_acc_bytes) : nullptr;
-  prm.num_chunks = pl.num_chunks;
+  prm.ws_acc = pl.ws_acc_bytes ? reinterpret_cast<float*>(base) : nullptr;
+  prm.ws_ml = pl.ws_ml_bytes ? reinterpret_cast<float*>(base + pl.ws_acc_bytes) : nullptr;
 }
 
 static int check_common(int dtype, int head_size, int block_size) {
@@ -594,16 +546,6 @@ static Plan plan_of(const mux_attn_mixed_args_t* a) {
                    a->num_stages, a->flags);
 }
 
-// The scheduling words must be zero at launch.  A caller that keeps its workspace to these
-// calls (zeroed once, never written by anything else) says so with MUX_ATTN_WORKSPACE_CLEAN;
-// otherwise they are cleared here, on the stream, before the launch.
-static int prepare_sched(const Plan& pl, long long items, void* workspace, int flags, cudaStream_t stream) {
-  if (!pl.persistent || (flags & MUX_ATTN_WORKSPACE_CLEAN)) return MUX_OK;
-  const size_t words = 2 + (size_t)items * pl.head_tiles;
-  cudaError_t e = cudaMemsetAsync(workspace, 0, words * 4, stream);
-  return e == cudaSuccess ? MUX_OK : record_cuda_error(e);
-}
-
 static int check_workspace(const Plan& pl, const void* workspace, size_t workspace_bytes) {
   const size_t need = pl.total();
   if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return MUX_ERR_WORKSPACE_TOO_SMALL;
@@ -633,7 +575,7 @@ struct NewRows {  // the decode step's new K/V rows; k == nullptr: plain attenti
 static int validate_new_rows(const NewRows& n, int flags) {
   if (n.k == nullptr && n.v == nullptr) return MUX_OK;
   if (n.k == nullptr || n.v == nullptr) return MUX_ERR_NULL_POINTER;
-  if (flags & MUX_ATTN_PERSISTENT) return MUX_ERR_BAD_SHAPE;
+  (void)flags;
   if (!aligned16(n.k) || !aligned16(n.v)) return MUX_ERR_MISALIGNED;
   if ((n.k_s0 & 7) || (n.k_s1 & 7) || (n.v_s0 & 7) || (n.v_s1 & 7)) return MUX_ERR_MISALIGNED;
   return MUX_OK;
@@ -678,7 +620,6 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.max_parts = pl.max_parts;
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
-  prm.num_items = (int)items;
   prm.k_new = rows.k;
   prm.v_new = rows.v;
   prm.kn_s0 = rows.k_s0;
@@ -686,7 +627,6 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.vn_s0 = rows.v_s0;
   prm.vn_s1 = rows.v_s1;
   mux::bind_workspace(prm, pl, workspace);
-  if ((st = mux::prepare_sched(pl, items, workspace, a->flags, static_cast<cudaStream_t>(cuda_stream))) != MUX_OK) return st;
   return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
                             static_cast<cudaStream_t>(cuda_stream));
 }
@@ -756,13 +696,11 @@ static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* 
   prm.max_parts = pl.max_parts;
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
-  prm.num_items = a->num_items;
   prm.k_new = rows.k;
   prm.v_new = rows.v;
   prm.kn_s0 = rows.k_s0;
   prm.vn_s0 = rows.v_s0;
   mux::bind_workspace(prm, pl, workspace);
-  if ((st = mux::prepare_sched(pl, a->num_items, workspace, a->flags, static_cast<cudaStream_t>(cuda_stream))) != MUX_OK) return st;
   return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
                            static_cast<cudaStream_t>(cuda_stream));
 }
@@ -797,10 +735,9 @@ int mux_decode_attention_mixed(const mux_decode_mixed_args_t* a, void* workspace
 // serving worker whose memory budget was fixed at start-up (FlexStore gives the
 // KV pool a set fraction of HBM and the rest is spoken for), a process that
 // shares the GPU with others under MPS and must not grow, or code on a path
-// where allocation calls are simply not allowed.  For them the scratch of the
-// launch (scheduling words and flash-decoding partials) lives in a fixed array
-// inside the library image instead of a caller buffer.  Every GPU that loads the
-// library carries the array until the process exits.
+// where allocation calls are simply not allowed.  For them the split-K scratch
+// lives in a fixed array inside the library image instead of a caller buffer.
+// Every GPU that loads the library carries the array until the process exits.
 namespace mux {
 
 constexpr size_t kStaticScratchBytes = MUX_STATIC_SCRATCH_BYTES;
@@ -839,10 +776,7 @@ extern "C" int mux_paged_attention_static_scratch(const mux_attn_args_t* a, void
   void* scratch = nullptr;
   st = mux::static_scratch_address(&scratch);
   if (st != MUX_OK) return st;
-  // Nothing in the scratch has to be cleared by the caller: the array starts
-  // zero-filled, the kernel puts its scheduling words back to zero before it
-  // ends, and every partial that is read was written earlier in the same launch.
-  mux_attn_args_t b = *a;
-  b.flags |= MUX_ATTN_WORKSPACE_CLEAN;
-  return mux_paged_attention(&b, scratch, mux::kStaticScratchBytes, cuda_stream);
+  // Nothing in the scratch has to be cleared: every partial that the merge kernel
+  // reads is written by the attention kernel of the same call first.
+  return mux_paged_attention(a, scratch, mux::kStaticScratchBytes, cuda_stream);
 }

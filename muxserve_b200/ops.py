@@ -78,15 +78,13 @@ def _stream() -> int:
 
 
 def _workspace(nbytes: int, device: torch.device) -> Optional[torch.Tensor]:
-    """Scratch of the attention launches (scheduling words + flash-decoding partials), cached per
-    (device, stream).  It is zero-filled when created and only these ops touch it, which is what
-    MUX_ATTN_WORKSPACE_CLEAN promises to the library."""
+    """Scratch for partitioned (flash-decoding) launches, cached per (device, stream)."""
     if nbytes == 0:
         return None
     key = (device.index, _stream())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -190,7 +188,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(),
         scale=float(scale), num_seqs=S, num_q_heads=Hq, num_kv_heads=H, head_size=HEAD_SIZE,
         block_size=block_size, max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages, flags=flags | _lib.MUX_ATTN_WORKSPACE_CLEAN)
+        partition_size=partition_size, num_stages=num_stages, flags=flags)
     L = lib()
     need = L.mux_paged_attention_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
@@ -211,7 +209,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         check(L.mux_decode_attention(C.byref(dargs), ws.data_ptr() if ws is not None else None,
                                      ws.numel() if ws is not None else 0, _stream()), "decode_attention")
     global launch_count
-    launch_count += 0 if S == 0 else (2 if not (flags & _lib.MUX_ATTN_PERSISTENT) and max_context_len > (partition_size or 512) else 1)
+    launch_count += 0 if S == 0 else (2 if need > 0 else 1)
 
 
 def decode_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
@@ -273,7 +271,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
         item_group=item_group.data_ptr(), item_scale=item_scale.data_ptr(),
         num_items=n, max_group=max_group, head_size=HEAD_SIZE, block_size=block_size,
         max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages, flags=flags | _lib.MUX_ATTN_WORKSPACE_CLEAN)
+        partition_size=partition_size, num_stages=num_stages, flags=flags)
     L = lib()
     need = L.mux_paged_attention_mixed_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
@@ -292,15 +290,9 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                                            ws.numel() if ws is not None else 0, _stream()),
               "decode_attention_mixed")
     global launch_count
-    launch_count += 0 if n == 0 else (2 if not (flags & _lib.MUX_ATTN_PERSISTENT) and max_context_len > (partition_size or 512) else 1)
+    launch_count += 0 if n == 0 else (2 if need > 0 else 1)
 
 
 def device_status() -> int:
-    """Reads and clears the MUX_DEV_* status bits of the current device (synchronises the stream).
-    After a non-zero status the cached workspaces are zero-filled again (a launch that gave up
-    on a wait may have left its scheduling words behind)."""
-    st = check(lib().mux_device_status(_stream()), "device_status")
-    if st:
-        for ws in _workspaces.values():
-            ws.zero_()
-    return st
+    """Reads and clears the MUX_DEV_* status bits of the current device (synchronises the stream)."""
+    return check(lib().mux_device_status(_stream()), "device_status")

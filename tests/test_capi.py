@@ -60,11 +60,7 @@ def test_validation_happens_before_any_launch(built_lib):
     a.q, a.max_context_len, a.partition_size = 0x1000, 4096, 512
     need = L.mux_paged_attention_workspace_size(C.byref(a))
     partials = (4 * 4) * 8 * 3 * (128 + 2) * 4                              # items x partitions x group x (acc + m,l) fp32
-    sched = ((2 + 65536) * 4 + 255) // 256 * 256                           # fixed region of scheduling words
-    assert need == sched + partials
-    a.flags = _lib.MUX_ATTN_PERSISTENT
-    assert L.mux_paged_attention_workspace_size(C.byref(a)) == need         # same layout for both launch schemes
-    a.flags = 0
+    assert need == partials
     assert L.mux_paged_attention(C.byref(a), None, 0, None) == -8          # workspace missing
     a.partition_size = 100
     assert L.mux_paged_attention(C.byref(a), None, 0, None) == -6          # not a multiple of block_size

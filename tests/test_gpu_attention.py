@@ -27,30 +27,28 @@ def run(ops, gu, case, kc, vc, head_mapping=None, **kw):
     return out
 
 
-@pytest.mark.parametrize("flags", [0, 1], ids=["grid_per_unit", "persistent"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B", [16, 8, 32])
 @pytest.mark.parametrize("group", [1, 8])
-def test_attention_ragged(env, dtype, B, group, flags):
+def test_attention_ragged(env, dtype, B, group):
     ops, gu = env
     ctx = [1, 2, B - 1, B, B + 1, 255, 256, 257, 300, 511, 77, 1000]
     H = 3
     case, kc, vc = gu.make_case(len(ctx), H * group, H, ctx, B, dtype, seed=3 + B + group, num_blocks=2048)
-    out = run(ops, gu, case, kc, vc, flags=flags)
+    out = run(ops, gu, case, kc, vc)
     kc_c, vc_c, ref = gu.oracle_step(case, kc, vc)
     assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
     gu.assert_close(out, ref, f"B={B} G={group} {dtype}")
     assert ops.device_status() == 0
 
 
-@pytest.mark.parametrize("flags", [0, 1], ids=["grid_per_unit", "persistent"])
 @pytest.mark.parametrize("psize,stages", [(16, 4), (64, 4), (128, 8), (512, 8), (1024, 12), (4096, 16)])
-def test_attention_partition_sizes(env, psize, stages, flags):
+def test_attention_partition_sizes(env, psize, stages):
     """Every partitioning gives the same answer (single partition up to 63 partitions per sequence)."""
     ops, gu = env
     ctx = [1000, 17, 513, 64, 2, 999]
     case, kc, vc = gu.make_case(len(ctx), 4, 4, ctx, 16, torch.float16, seed=21, num_blocks=1024)
-    out = run(ops, gu, case, kc, vc, partition_size=psize, num_stages=stages, flags=flags)
+    out = run(ops, gu, case, kc, vc, partition_size=psize, num_stages=stages)
     _, _, ref = gu.oracle_step(case, kc, vc)
     gu.assert_close(out, ref, f"partition {psize}")
     assert ops.device_status() == 0
@@ -166,16 +164,15 @@ def test_attention_known_answers(env):
     assert torch.allclose(out[2, 4].float().cpu(), v.mean(0), atol=2e-3, rtol=1e-2)
 
 
-def test_attention_many_units_per_cta_and_repeated_launches(env):
-    """More work units than resident CTAs (every CTA loops over many units) and back-to-back launches
-    on one workspace: scheduling words must come back clean each time."""
+def test_attention_many_partitions_and_repeated_launches(env):
+    """Thousands of small partitions, launched back to back on one workspace."""
     ops, gu = env
     gen = torch.Generator().manual_seed(5)
     ctx = torch.randint(1, 400, (192,), generator=gen).tolist()
     case, kc, vc = gu.make_case(len(ctx), 8, 8, ctx, 16, torch.float16, seed=77, num_blocks=40000)
     _, _, ref = gu.oracle_step(case, kc, vc)
     for rep in range(3):
-        out = run(ops, gu, case, kc, vc, partition_size=32, flags=1)  # persistent: ~ 10k units on ~ 900 CTAs
+        out = run(ops, gu, case, kc, vc, partition_size=32)
         gu.assert_close(out, ref, f"repeat {rep}")
     assert ops.device_status() == 0
 
@@ -207,8 +204,8 @@ def test_fused_decode_step_equals_two_ops(env, dtype, B, group, psize):
 
 
 def test_attention_dirty_workspace_through_c_abi(env, built_lib):
-    """Straight through the C ABI with a caller workspace full of garbage and no CLEAN flag:
-    the library clears the scheduling words itself."""
+    """Straight through the C ABI with a caller workspace full of garbage: nothing in it needs
+    to be initialised."""
     import ctypes as C
     ops, gu = env
     from muxserve_b200 import _lib
@@ -223,8 +220,7 @@ def test_attention_dirty_workspace_through_c_abi(env, built_lib):
         value_cache=vc.data_ptr(), num_blocks=kc.shape[0], head_mapping=None, block_tables=bt.data_ptr(),
         bt_seq_stride=bt.stride(0), bt_head_stride=bt.stride(1), context_lens=case.context_lens.data_ptr(),
         scale=case.scale, num_seqs=len(ctx), num_q_heads=8, num_kv_heads=2, head_size=128, block_size=16,
-        max_context_len=case.max_context_len, dtype=_lib.MUX_DTYPE_F16, partition_size=64, num_stages=0,
-        flags=_lib.MUX_ATTN_PERSISTENT)
+        max_context_len=case.max_context_len, dtype=_lib.MUX_DTYPE_F16, partition_size=64, num_stages=0, flags=0)
     need = built_lib.mux_paged_attention_workspace_size(C.byref(a))
     ws = torch.full((need,), 0xA5, dtype=torch.uint8, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
@@ -233,7 +229,6 @@ def test_attention_dirty_workspace_through_c_abi(env, built_lib):
     torch.cuda.synchronize()
     _, _, ref = gu.oracle_step(case, kc, vc)
     gu.assert_close(out, ref, "dirty workspace")
-    assert int(ws[:8].view(torch.int32).abs().sum()) == 0          # queue and exit words are back to zero
     assert ops.device_status() == 0
 
 
