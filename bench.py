@@ -505,8 +505,11 @@ def run_native_c3(args):
     plan = mixed.build_mixed_plan(batches, dev)
     L_max = max(plan.layers)
     packed_q = [mixed.pack_rows(plan, [c.q[i % c.q.shape[0]] for c in cases]) for i in range(4)]
+    packed_k = [mixed.pack_rows(plan, [c.k[i % c.k.shape[0]] for c in cases]) for i in range(4)]
+    packed_v = [mixed.pack_rows(plan, [c.v[i % c.v.shape[0]] for c in cases]) for i in range(4)]
     out = torch.empty_like(packed_q[0])
     psize, nst = args.partition_size, args.num_stages
+    fused = not args.two_op
     attn_bytes, cw_bytes = [], []
     for l in range(L_max):
         a = w = 0
@@ -519,17 +522,22 @@ def run_native_c3(args):
 
     def step(events=None):
         for l in range(L_max):
-            for c in cases:
-                if c.shape.num_layers > l:
-                    r = l % c.k.shape[0]
-                    ops.reshape_and_cache(c.k[r], c.v[r], kc, vc, c.slot_mapping[:, l, :])
             n_items, n_rows = plan.active(l)
+            new_kv = {}
+            if fused:      # one launch per layer index: every model's cache write and attention
+                new_kv = dict(new_k=packed_k[l % 4][:n_items], new_v=packed_v[l % 4][:n_items])
+            else:
+                for c in cases:
+                    if c.shape.num_layers > l:
+                        r = l % c.k.shape[0]
+                        ops.reshape_and_cache(c.k[r], c.v[r], kc, vc, c.slot_mapping[:, l, :])
             if events is not None:
                 events[l][0].record()
             ops.paged_attention_mixed(out[:n_rows], packed_q[l % 4][:n_rows], kc, vc, plan.block_tables[l, :n_items],
                                       plan.item_context_len[:n_items], plan.item_q_row[:n_items],
                                       plan.item_group[:n_items], plan.item_scale[:n_items], BLOCK,
-                                      plan.max_context_len, plan.max_group, partition_size=psize, num_stages=nst)
+                                      plan.max_context_len, plan.max_group, partition_size=psize, num_stages=nst,
+                                      **new_kv)
             if events is not None:
                 events[l][1].record()
 
@@ -569,7 +577,9 @@ def run_native_c3(args):
             "config": {"workload": "c3: " + C3_DESC, "block_size": BLOCK, "seed": args.seed,
                        "pool": f"{num_blocks} blocks = {num_blocks * 8192 / 1e9:.1f} GB ({args.pool_frac:.0%} of HBM)",
                        "items_per_launch": plan.item_offset, "layers": plan.layers,
-                       "placement": "one TP=4 rank's share per GPU; value counts each GPU's share as its own batch"},
+                       "placement": "one TP=4 rank's share per GPU; value counts each GPU's share as its own batch",
+                       "step": ("one fused launch per layer index (all models' cache writes + attention)" if fused else
+                                "one reshape_and_cache per model and layer + one fused attention launch per layer index")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "kernel": "paged_attn_kernel<mixed> (+ merge)",
                          "algorithmic_bytes_per_step": sum(attn_bytes), "attention_ms_per_step": attn_ms,
