@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiler captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small profiler captures)")
     ap.add_argument("--seed", type=int, default=20240531)
+    ap.add_argument("--eager", action="store_true",
+                    help="time Python-issued launches instead of replaying a CUDA graph of one step")
     ap.add_argument("--two-op", action="store_true",
                     help="time reshape_and_cache + paged_attention as separate calls instead of the fused decode step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -323,19 +325,47 @@ def run_native(args):
               for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local_rank)
+    graph = None
+    if not args.eager:
+        torch.cuda.synchronize()
+        l0 = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        per_step_launches = ops.launch_count - l0
+        graph.replay()
     barrier()
     sampler.start()
     launches0 = ops.launch_count
     e0.record()
     for i in range(args.steps):
-        step(events[i])
+        if graph is not None:
+            graph.replay()
+        else:
+            step(events[i])
     e1.record()
-    gpu_launches = ops.launch_count - launches0
+    gpu_launches = ops.launch_count - launches0 if graph is None else per_step_launches * args.steps
     barrier()
     clocks = sampler.stop()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
-    attn_ms = sum(a.elapsed_time(b) for evs in events for a, b in evs) / (args.steps * L)
+    if graph is not None:
+        # the kernel-level span cannot be bracketed inside a graph: a second, eager pass of the same
+        # steps with CUDA events around every attention launch gives it
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step(events[i])
+        e1.record()
+        barrier()
+        ms_eager = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    else:
+        ms_eager = ms_step
+    eager_span_ms = sum(a.elapsed_time(b) for evs in events for a, b in evs) / (args.steps * L)
+    # Under graph replay with the fused step a layer IS one attention launch (+ its merge kernel), so
+    # step time / layers bounds the launch duration from above, gaps included, without the extra
+    # serialisation that event records between the launches of the eager pass introduce.
+    attn_ms = ms_step / L if (graph is not None and fused) else eager_span_ms
     status = ops.device_status() | status_warm
 
     # ---- the same step with the two reference-signature ops (separate cache-write launch) ----
@@ -343,10 +373,18 @@ def run_native(args):
     if fused:
         for _ in range(3):
             step(fuse=False)
+        run2 = lambda: step(fuse=False)
+        if not args.eager:
+            torch.cuda.synchronize()
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2):
+                step(fuse=False)
+            run2 = g2.replay
+            run2()
         barrier()
         e0.record()
         for _ in range(args.steps):
-            step(fuse=False)
+            run2()
         e1.record()
         barrier()
         ms2 = max_over_ranks(e0.elapsed_time(e1)) / args.steps
@@ -451,15 +489,22 @@ def run_native(args):
                              "blocks, far above the 126 MB L2",
                        "placement": ("1 model on 1 GPU" if world == 1 else
                                      f"{world} independent model replicas, one per GPU, no data-path collective"),
-                       "partition_size": psize or "library default", "num_stages": nst or "library default"},
+                       "partition_size": psize or "library default", "num_stages": nst or "library default",
+                       "launch": "CUDA graph replay of one step" if graph is not None else "eager (Python call per op)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic,
                          "kernel": ("paged_attn_kernel<fused cache write> (+ merge kernel)" if fused else
                                     "paged_attn_kernel (+ merge kernel)"),
                          "algorithmic_bytes_per_launch": launch_bytes, "avg_launch_ms": attn_ms,
-                         "peak_source": peak_src, "whole_path_gbs": path_gbs},
+                         "peak_source": peak_src, "whole_path_gbs": path_gbs,
+                         "whole_path_frac": path_gbs / peak,
+                         "span": ("timed region / launches (graph replay, one attention launch per layer)"
+                                  if (graph is not None and fused) else
+                                  "CUDA events around every attention launch"),
+                         "eager_span_ms": eager_span_ms},
             "step": ("decode_attention per layer (cache write fused into the attention launch)" if fused else
                      "reshape_and_cache + paged_attention per layer"),
+            "eager_ms_per_step": ms_eager,
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
             "clocks": clocks, "device_status": status,
         }
@@ -552,18 +597,40 @@ def run_native_c3(args):
               for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local_rank)
+    graph = None
+    if not args.eager:
+        torch.cuda.synchronize()
+        l0 = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        per_step_launches = ops.launch_count - l0
+        graph.replay()
     barrier()
     sampler.start()
     launches0 = ops.launch_count
     e0.record()
     for i in range(args.steps):
-        step(events[i])
+        if graph is not None:
+            graph.replay()
+        else:
+            step(events[i])
     e1.record()
-    gpu_launches = ops.launch_count - launches0
+    gpu_launches = ops.launch_count - launches0 if graph is None else per_step_launches * args.steps
     barrier()
     clocks = sampler.stop()
     from muxserve_b200.parallel import max_over_ranks
     ms_step = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    if graph is not None:
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step(events[i])
+        e1.record()
+        barrier()
+        ms_eager = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    else:
+        ms_eager = ms_step
     attn_ms = sum(a.elapsed_time(b) for evs in events for a, b in evs) / args.steps     # all layers of a step
     status = ops.device_status()
     if rank == 0:
@@ -577,6 +644,7 @@ def run_native_c3(args):
             "config": {"workload": "c3: " + C3_DESC, "block_size": BLOCK, "seed": args.seed,
                        "pool": f"{num_blocks} blocks = {num_blocks * 8192 / 1e9:.1f} GB ({args.pool_frac:.0%} of HBM)",
                        "items_per_launch": plan.item_offset, "layers": plan.layers,
+                       "launch": "CUDA graph replay of one step" if graph is not None else "eager (Python call per op)",
                        "placement": "one TP=4 rank's share per GPU; value counts each GPU's share as its own batch",
                        "step": ("one fused launch per layer index (all models' cache writes + attention)" if fused else
                                 "one reshape_and_cache per model and layer + one fused attention launch per layer index")},
@@ -586,6 +654,7 @@ def run_native_c3(args):
                          "peak_source": peak_src,
                          "whole_path_gbs": (sum(attn_bytes) + sum(cw_bytes)) / (ms_step * 1e-3) / 1e9},
             "cpu_baseline": None, "e2e": None, "gpu_launches": gpu_launches, "clocks": clocks, "device_status": status,
+            "eager_ms_per_step": ms_eager,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
