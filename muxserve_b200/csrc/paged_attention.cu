@@ -32,7 +32,7 @@ namespace mux {
 // also appends the item's new token: it patches the staged copy of the last K and V block in
 // shared memory with the new rows (so the attention sees them) and writes them to the pool.
 template <typename T, int BS, bool MIXED, bool FUSE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 6)  // six CTAs per SM: at most 64 registers per thread
 paged_attn_kernel(const __grid_constant__ AttnParams p) {
   constexpr int TILE = kHeadSize * BS * 2;       // bytes of one K or V block
   constexpr int MT = BS >= 16 ? BS / 16 : 1;     // 16-token m-tiles per K block
