@@ -404,17 +404,32 @@ def run_native(args):
         smh = pin(case.slot_mapping[:, rep, :].contiguous())
         ch = pin(case.context_lens)
         oh = torch.empty((L, S, Hq, 128), dtype=dt).pin_memory()
+        run_e2e = lambda: hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len)
         for _ in range(3):
-            hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len)
+            run_e2e()
+        e2e_mode = "eager"
+        if not args.eager:
+            # the whole host-driven step (copies on their streams + launches) as one CUDA graph
+            try:
+                torch.cuda.synchronize()
+                ge = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(ge):
+                    run_e2e()
+                ge.replay()
+                torch.cuda.synchronize()
+                run_e2e, e2e_mode = ge.replay, "CUDA graph replay (copies and launches captured together)"
+            except Exception as exc:   # capture of the multi-stream step refused: keep the eager pipeline
+                e2e_mode = f"eager (graph capture failed: {type(exc).__name__})"
+                torch.cuda.synchronize()
         barrier()
         e0.record()
         for _ in range(args.steps):
-            hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len)
+            run_e2e()
         e1.record()
         barrier()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
         e2e = {"value": world * S / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": hs.h2d_bytes, "d2h_bytes_per_step": hs.d2h_bytes,
+               "h2d_bytes_per_step": hs.h2d_bytes, "d2h_bytes_per_step": hs.d2h_bytes, "launch": e2e_mode,
                "how": "HostDecodeStep.run: pinned host q/k/v/block_tables/slot_mapping/context_lens -> device, "
                       "ops, out -> pinned host, per layer on copy streams overlapped with the kernels"}
         status |= ops.device_status()
