@@ -48,9 +48,9 @@ C3_DESC = ("three colocated LLaMA models (7B/13B/30B: 32/40/52 heads, 32/40/60 l
 BLOCK = 16
 DTYPES = {"f16": torch.float16, "bf16": torch.bfloat16}
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_kernel launch, from the ncu capture summarised in
-# profiles/paged_attn_kernel_c2_small.md (same per-launch work as the benchmark's layer, smaller pool).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 1202712000 + 6585344}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused decode kernel, from the ncu capture
+# summarised in profiles/paged_attn_kernel_c2_fused_small.md (same per-launch work as a layer of c2, smaller pool).
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 1203705000 + 12956160}
 
 
 def parse_args():
