@@ -444,7 +444,11 @@ def run_native(args):
         def tp_step(allreduce=True, attention=True):
             for l in range(L):
                 r = l % L_res
-                if attention:
+                if attention and fused:
+                    ops.decode_attention(out[:, :Hql], case.q[r][:, :Hql], case.k[r][:, :Hl], case.v[r][:, :Hl], kc, vc,
+                                         None, case.scale, case.block_tables[r][:, :Hl], case.context_lens, BLOCK,
+                                         case.max_context_len, partition_size=psize, num_stages=nst)
+                elif attention:
                     ops.reshape_and_cache(case.k[r][:, :Hl], case.v[r][:, :Hl], kc, vc, case.slot_mapping[:, r, :Hl])
                     ops.paged_attention(out[:, :Hql], case.q[r][:, :Hql], kc, vc, None, case.scale,
                                         case.block_tables[r][:, :Hl], case.context_lens, BLOCK, case.max_context_len,
@@ -452,13 +456,29 @@ def run_native(args):
                 if allreduce:
                     dist.all_reduce(full)
 
+        tp_mode = "eager"
+
         def timed(fn):
+            nonlocal tp_mode
             for _ in range(3):
                 fn()
+            run = fn
+            if not args.eager:      # kernels and NCCL all-reduces of one step as one CUDA graph
+                try:
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        fn()
+                    g.replay()
+                    torch.cuda.synchronize()
+                    run, tp_mode = g.replay, "CUDA graph replay"
+                except Exception as exc:
+                    tp_mode = f"eager (graph capture failed: {type(exc).__name__})"
+                    torch.cuda.synchronize()
             barrier()
             e0.record()
             for _ in range(args.steps):
-                fn()
+                run()
             e1.record()
             barrier()
             return max_over_ranks(e0.elapsed_time(e1)) / args.steps
@@ -468,7 +488,7 @@ def run_native(args):
         ms_at = timed(lambda: tp_step(allreduce=False))
         tp = {"tp": world, "scaling": "strong", "tokens_per_s": S / (ms_tp * 1e-3), "ms_per_step": ms_tp,
               "attention_only_ms_per_step": ms_at, "allreduce_only_ms_per_step": ms_ar,
-              "allreduce_bytes": full.numel() * full.element_size(),
+              "allreduce_bytes": full.numel() * full.element_size(), "launch": tp_mode,
               "note": "kv heads sharded over ranks (no cross-GPU traffic in attention); one NCCL all-reduce of the "
                       "[batch, hidden] output per layer"}
 
