@@ -224,6 +224,8 @@ typedef struct {
   int64_t k_head_stride;
   int64_t v_seq_stride;
   int64_t v_head_stride;
+  const void* cos_sin_cache; /* NULL, or rotary cache [max_position][64 cos | 64 sin] in the tensor dtype: q and the */
+  int64_t max_position;      /* new k are rotated at position context_len - 1 first (see mux_rotary_embedding) */
 } mux_decode_args_t;
 
 /* workspace: mux_paged_attention_workspace_size(&args->attn) */
@@ -236,11 +238,32 @@ typedef struct {
   const void* v;
   int64_t k_row_stride;     /* elements */
   int64_t v_row_stride;
+  const void* cos_sin_cache; /* as in mux_decode_args_t; one cache for all models of the launch */
+  int64_t max_position;
 } mux_decode_mixed_args_t;
 
 /* workspace: mux_paged_attention_mixed_workspace_size(&args->attn) */
 int mux_decode_attention_mixed(const mux_decode_mixed_args_t* args, void* workspace,
                                size_t workspace_bytes, void* cuda_stream);
+
+/* ------------------------------------------------------------------------
+ * rotary position embedding of q and k, in place — the step PagedAttentionWithRoPE applies before
+ * the cache write (parameters at muxserve/flexserver/models/llama.py:138-147: rotary_dim = head
+ * size, GPT-NeoX pairing of element d with d + 64).  fp32 arithmetic, one rounding.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  void* q;                    /* [num_tokens, num_q_heads, 128], may be NULL when num_q_heads == 0 */
+  void* k;                    /* [num_tokens, num_kv_heads, 128] */
+  int64_t q_token_stride, q_head_stride, k_token_stride, k_head_stride;   /* elements */
+  const int64_t* positions;   /* [num_tokens] device */
+  const void* cos_sin_cache;  /* [max_position][64 cos | 64 sin], tensor dtype, device */
+  int64_t max_position;
+  int32_t num_tokens, num_q_heads, num_kv_heads, head_size;
+  int32_t dtype;
+  int32_t reserved;
+} mux_rotary_args_t;
+
+int mux_rotary_embedding(const mux_rotary_args_t* args, void* cuda_stream);
 
 /* Reads and clears the device status word (MUX_DEV_* bits) of the current
  * device.  Synchronises the given stream. Returns a negative mux_status_t on failure. */

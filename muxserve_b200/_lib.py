@@ -20,7 +20,7 @@ MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class CacheWriteArgs(C.Structure):
@@ -78,6 +78,7 @@ class DecodeArgs(C.Structure):
         ("attn", AttnArgs), ("k", C.c_void_p), ("v", C.c_void_p),
         ("k_seq_stride", C.c_int64), ("k_head_stride", C.c_int64),
         ("v_seq_stride", C.c_int64), ("v_head_stride", C.c_int64),
+        ("cos_sin_cache", C.c_void_p), ("max_position", C.c_int64),
     ]
 
 
@@ -85,6 +86,18 @@ class DecodeMixedArgs(C.Structure):
     _fields_ = [
         ("attn", AttnMixedArgs), ("k", C.c_void_p), ("v", C.c_void_p),
         ("k_row_stride", C.c_int64), ("v_row_stride", C.c_int64),
+        ("cos_sin_cache", C.c_void_p), ("max_position", C.c_int64),
+    ]
+
+
+class RotaryArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p),
+        ("q_token_stride", C.c_int64), ("q_head_stride", C.c_int64),
+        ("k_token_stride", C.c_int64), ("k_head_stride", C.c_int64),
+        ("positions", C.c_void_p), ("cos_sin_cache", C.c_void_p), ("max_position", C.c_int64),
+        ("num_tokens", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_size", C.c_int32),
+        ("dtype", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -104,6 +117,7 @@ SIGNATURES = {
     "mux_paged_attention_mixed": (C.c_int, [C.POINTER(AttnMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_decode_attention": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_decode_attention_mixed": (C.c_int, [C.POINTER(DecodeMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mux_rotary_embedding": (C.c_int, [C.POINTER(RotaryArgs), C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),
     "mux_kv_storage_create": (C.c_void_p, [C.c_int32]),
     "mux_kv_storage_destroy": (None, [C.c_void_p]),

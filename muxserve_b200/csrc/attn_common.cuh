@@ -5,6 +5,7 @@
 
 #include "internal.h"
 #include "ptx.cuh"
+#include "rope.cuh"
 
 namespace mux {
 
@@ -47,6 +48,8 @@ struct AttnParams {
   const void* k_new;
   const void* v_new;
   long long kn_s0, kn_s1, vn_s0, vn_s1;  // single model: seq, head strides; mixed: s0 = item (row) stride
+  const void* rope_cache;                // fused decode step only: [max_position][64 cos | 64 sin], or nullptr
+  long long rope_max_position;
 };
 
 // Shared-memory carve-up, identical on host (sizing) and device.

@@ -125,11 +125,22 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   const int* ids_c = reinterpret_cast<const int*>(smem + L.ids);
   uint4 knew = make_uint4(0u, 0u, 0u, 0u);
   uint2 vnew = make_uint2(0u, 0u);
+  // Rotary embedding of the decode step: the query and the new key sit at position ctx - 1.
+  const T* rope_row = nullptr;
+  if (FUSE && p.rope_cache != nullptr) {
+    long long pos = d.ctx - 1;
+    if (pos >= p.rope_max_position) {
+      if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
+      pos = p.rope_max_position - 1;
+    }
+    rope_row = static_cast<const T*>(p.rope_cache) + pos * kHeadSize;
+  }
   if (appends) {
     const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
     const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
     if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
     vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
+    if (rope_row != nullptr) knew = rope_row16<T>(knew, lane, rope_row);  // rotary at position ctx - 1
   }
 
   // q as the B operand (k = d, n = head): b0 = q[g][16ks + 2tq, +1], b1 = q[g][16ks + 8 + 2tq, +1]
@@ -142,6 +153,15 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       for (int ks = 0; ks < 8; ++ks) {
         qf[ks][0] = ldg32_nc(qr + ks * 16 + 2 * tq);
         qf[ks][1] = ldg32_nc(qr + ks * 16 + 8 + 2 * tq);
+      }
+      if (FUSE && rope_row != nullptr) {  // element d < 64 is in qf[ks][r], its partner d + 64 in qf[ks + 4][r]
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int dd = ks * 16 + r * 8 + 2 * tq;
+            rope_words<T>(qf[ks][r], qf[ks + 4][r], ldg32_nc(rope_row + dd), ldg32_nc(rope_row + 64 + dd));
+          }
       }
     } else {
 #pragma unroll
@@ -570,6 +590,8 @@ struct NewRows {  // the decode step's new K/V rows; k == nullptr: plain attenti
   const void* k = nullptr;
   const void* v = nullptr;
   long long k_s0 = 0, k_s1 = 0, v_s0 = 0, v_s1 = 0;
+  const void* rope_cache = nullptr;   // optional rotary embedding of q and the new k
+  long long rope_max_position = 0;
 };
 
 static int validate_new_rows(const NewRows& n, int flags) {
@@ -578,6 +600,7 @@ static int validate_new_rows(const NewRows& n, int flags) {
   (void)flags;
   if (!aligned16(n.k) || !aligned16(n.v)) return MUX_ERR_MISALIGNED;
   if ((n.k_s0 & 7) || (n.k_s1 & 7) || (n.v_s0 & 7) || (n.v_s1 & 7)) return MUX_ERR_MISALIGNED;
+  if (n.rope_cache != nullptr && (!aligned16(n.rope_cache) || n.rope_max_position <= 0)) return MUX_ERR_BAD_SHAPE;
   return MUX_OK;
 }
 
@@ -626,6 +649,8 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.kn_s1 = rows.k_s1;
   prm.vn_s0 = rows.v_s0;
   prm.vn_s1 = rows.v_s1;
+  prm.rope_cache = rows.rope_cache;
+  prm.rope_max_position = rows.rope_max_position;
   mux::bind_workspace(prm, pl, workspace);
   return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
                             static_cast<cudaStream_t>(cuda_stream));
@@ -651,6 +676,8 @@ int mux_decode_attention(const mux_decode_args_t* a, void* workspace, size_t wor
   rows.k_s1 = a->k_head_stride;
   rows.v_s0 = a->v_seq_stride;
   rows.v_s1 = a->v_head_stride;
+  rows.rope_cache = a->cos_sin_cache;
+  rows.rope_max_position = a->max_position;
   return mux::run_single(&a->attn, rows, workspace, workspace_bytes, cuda_stream);
 }
 
@@ -700,6 +727,8 @@ static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* 
   prm.v_new = rows.v;
   prm.kn_s0 = rows.k_s0;
   prm.vn_s0 = rows.v_s0;
+  prm.rope_cache = rows.rope_cache;
+  prm.rope_max_position = rows.rope_max_position;
   mux::bind_workspace(prm, pl, workspace);
   return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
                            static_cast<cudaStream_t>(cuda_stream));
@@ -723,6 +752,8 @@ int mux_decode_attention_mixed(const mux_decode_mixed_args_t* a, void* workspace
   rows.v = a->v;
   rows.k_s0 = a->k_row_stride;
   rows.v_s0 = a->v_row_stride;
+  rows.rope_cache = a->cos_sin_cache;
+  rows.rope_max_position = a->max_position;
   return mux::run_mixed(&a->attn, rows, workspace, workspace_bytes, cuda_stream);
 }
 

@@ -131,7 +131,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                     block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
                     max_context_len: int, *, num_kv_heads: Optional[int] = None,
                     partition_size: int = 0, num_stages: int = 0, flags: int = 0,
-                    _new_kv=None) -> None:
+                    _new_kv=None, _rope=None) -> None:
     """Decode attention of one query token per sequence over the paged pool.
 
     ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
@@ -204,27 +204,72 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
             raise ValueError(f"k and v must hold one new row per (sequence, kv head): [{S}, {H}, {HEAD_SIZE}]")
         if k.dtype != key_cache.dtype or v.dtype != key_cache.dtype:
             raise TypeError("k/v dtype differs from the pool dtype")
+        rope_ptr, rope_len = _rope_cache(_rope, q)
         dargs = _lib.DecodeArgs(attn=args, k=k.data_ptr(), v=v.data_ptr(), k_seq_stride=k_ss, k_head_stride=k_hs,
-                                v_seq_stride=v_ss, v_head_stride=v_hs)
+                                v_seq_stride=v_ss, v_head_stride=v_hs, cos_sin_cache=rope_ptr, max_position=rope_len)
         check(L.mux_decode_attention(C.byref(dargs), ws.data_ptr() if ws is not None else None,
                                      ws.numel() if ws is not None else 0, _stream()), "decode_attention")
     global launch_count
     launch_count += 0 if S == 0 else (2 if need > 0 else 1)
 
 
+def make_cos_sin_cache(max_position: int, base: float = 10000.0, dtype: torch.dtype = torch.float16,
+                       device="cuda") -> torch.Tensor:
+    """Rotary cache [max_position, 128] in the tensor dtype: 64 cosines then 64 sines of
+    position * base^(-2i/128) (rope_theta and max_position_embeddings of llama.py:138-147)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, HEAD_SIZE, 2, dtype=torch.float32) / HEAD_SIZE))
+    freqs = torch.outer(torch.arange(max_position, dtype=torch.float32), inv_freq)
+    return torch.cat([freqs.cos(), freqs.sin()], dim=-1).to(dtype).to(device).contiguous()
+
+
+def _rope_cache(cache: Optional[torch.Tensor], like: torch.Tensor):
+    if cache is None:
+        return None, 0
+    if (not cache.is_cuda or cache.dim() != 2 or cache.shape[1] != HEAD_SIZE or not cache.is_contiguous()
+            or cache.dtype != like.dtype):
+        raise ValueError(f"cos_sin_cache must be a contiguous CUDA [max_position, {HEAD_SIZE}] tensor of the q dtype")
+    return cache.data_ptr(), cache.shape[0]
+
+
+def rotary_embedding(positions: torch.Tensor, q: Optional[torch.Tensor], k: Optional[torch.Tensor],
+                     cos_sin_cache: torch.Tensor) -> None:
+    """In-place rotary embedding (GPT-NeoX pairing, rotary dimension 128) of ``q`` [T, Hq(*128)] and ``k``
+    [T, H(*128)] at ``positions`` (int64 [T]) — what PagedAttentionWithRoPE does before the cache write."""
+    ref = q if q is not None else k
+    _require_cuda(positions=positions, q=q, k=k, cos_sin_cache=cos_sin_cache)
+    rope_ptr, rope_len = _rope_cache(cos_sin_cache, ref)
+    if positions.dtype != torch.int64 or positions.dim() != 1 or not positions.is_contiguous():
+        raise TypeError("positions must be a contiguous int64 [tokens] tensor")
+    T = positions.shape[0]
+    Tq, Hq, q_ts, q_hs = _rows(q, "q") if q is not None else (T, 0, 0, 0)
+    Tk, Hk, k_ts, k_hs = _rows(k, "k") if k is not None else (T, 0, 0, 0)
+    if Tq != T or Tk != T:
+        raise ValueError("positions, q and k differ in the number of tokens")
+    args = _lib.RotaryArgs(q=q.data_ptr() if q is not None else None, k=k.data_ptr() if k is not None else None,
+                           q_token_stride=q_ts, q_head_stride=q_hs, k_token_stride=k_ts, k_head_stride=k_hs,
+                           positions=positions.data_ptr(), cos_sin_cache=rope_ptr, max_position=rope_len,
+                           num_tokens=T, num_q_heads=Hq, num_kv_heads=Hk, head_size=HEAD_SIZE,
+                           dtype=_dtype_code(ref, "q/k"), reserved=0)
+    check(lib().mux_rotary_embedding(C.byref(args), _stream()), "rotary_embedding")
+    global launch_count
+    launch_count += 1 if T > 0 and Hq + Hk > 0 else 0
+
+
 def decode_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                      key_cache: torch.Tensor, value_cache: torch.Tensor, head_mapping: Optional[torch.Tensor],
                      scale: float, block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
-                     max_context_len: int, **kw) -> None:
+                     max_context_len: int, *, cos_sin_cache: Optional[torch.Tensor] = None, **kw) -> None:
     """``reshape_and_cache`` + ``paged_attention`` of one layer's decode step in one launch.
 
     ``k``, ``v``: [S, H*128] or [S, H, 128], the new token of every sequence.  Row (s, h) is
     appended at position ``context_lens[s] - 1`` of block list ``block_tables[s, h]`` — the slot
     the reference's ``slot_mapping`` names for a decode step (csrc/batch_scheduler.h:58-67) — and
     attention runs over all ``context_lens[s]`` tokens.  Results equal the two separate ops bit for bit.
+    With ``cos_sin_cache`` the query and the new key are first rotated at position ``context_lens[s] - 1``
+    (neither ``q`` nor ``k`` is modified), as ``rotary_embedding`` would.
     """
     paged_attention(out, q, key_cache, value_cache, head_mapping, scale, block_tables, context_lens,
-                    block_size, max_context_len, _new_kv=(k, v), **kw)
+                    block_size, max_context_len, _new_kv=(k, v), _rope=cos_sin_cache, **kw)
 
 
 def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
@@ -233,7 +278,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                           item_group: torch.Tensor, item_scale: torch.Tensor, block_size: int,
                           max_context_len: int, max_group: int, *, partition_size: int = 0,
                           num_stages: int = 0, flags: int = 0, new_k: Optional[torch.Tensor] = None,
-                          new_v: Optional[torch.Tensor] = None) -> None:
+                          new_v: Optional[torch.Tensor] = None, cos_sin_cache: Optional[torch.Tensor] = None) -> None:
     """One launch for the decode batches of several models sharing the pool.
 
     Item ``i`` is one (sequence, kv head) of some model: q rows
@@ -284,8 +329,10 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
         for name, t in (("new_k", new_k), ("new_v", new_v)):
             if t.dim() != 2 or tuple(t.shape) != (n, HEAD_SIZE) or t.stride(1) != 1 or t.dtype != q.dtype:
                 raise ValueError(f"{name} must be [{n}, {HEAD_SIZE}] of the pool dtype with a dense last dim")
+        rope_ptr, rope_len = _rope_cache(cos_sin_cache, q)
         dargs = _lib.DecodeMixedArgs(attn=args, k=new_k.data_ptr(), v=new_v.data_ptr(),
-                                     k_row_stride=new_k.stride(0), v_row_stride=new_v.stride(0))
+                                     k_row_stride=new_k.stride(0), v_row_stride=new_v.stride(0),
+                                     cos_sin_cache=rope_ptr, max_position=rope_len)
         check(L.mux_decode_attention_mixed(C.byref(dargs), ws.data_ptr() if ws is not None else None,
                                            ws.numel() if ws is not None else 0, _stream()),
               "decode_attention_mixed")

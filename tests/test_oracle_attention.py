@@ -80,3 +80,19 @@ def test_algorithmic_bytes_formula():
     b = workloads.attention_bytes(ctx, 32, 32, 16)
     assert b == 32 * (128 + 2048) * 512 + 2 * 2 * 32 * 256 + 4 * 32 * (8 + 128) + 8
     assert workloads.cache_write_bytes(64, 32) == 4 * 64 * 32 * 256 + 8 * 64 * 32
+
+
+def test_rotary_oracle_properties():
+    from oracle.rotary_oracle import make_cos_sin_cache, rotary_ref
+    cache = make_cos_sin_cache(512)
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(5, 3, 128, generator=gen)
+    pos = torch.tensor([0, 1, 7, 100, 511])
+    y = rotary_ref(x, pos, cache)
+    assert torch.equal(y[0], x[0])                                             # position 0: identity
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-4)           # rotations keep the norm
+    # relative-position property: <R_p q, R_p' k> depends on p - p' only
+    q, k = x[1:2], x[2:3]
+    a = (rotary_ref(q, torch.tensor([10]), cache) * rotary_ref(k, torch.tensor([4]), cache)).sum()
+    b = (rotary_ref(q, torch.tensor([106]), cache) * rotary_ref(k, torch.tensor([100]), cache)).sum()
+    assert torch.allclose(a, b, atol=1e-3)
