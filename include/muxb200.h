@@ -126,6 +126,8 @@ typedef struct {
   int64_t bt_seq_stride;       /* elements */
   int64_t bt_head_stride;      /* elements; 0 = all kv heads share one list (plain vLLM layout) */
   const int32_t* context_lens; /* [num_seqs] device */
+  const int32_t* seq_rows;     /* NULL, or [num_seqs] device: sequence s uses row seq_rows[s] of block_tables
+                                  (a persistent table kept on the device, see mux_block_table_append) */
   float scale;
   int32_t num_seqs;
   int32_t num_q_heads;
@@ -264,6 +266,20 @@ typedef struct {
 } mux_rotary_args_t;
 
 int mux_rotary_embedding(const mux_rotary_args_t* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------
+ * Persistent block tables on the device.  The reference rebuilds and uploads the whole
+ * [L, S, H, max_blocks] table every step (csrc/batch_scheduler.cpp:156-169,
+ * muxserve/flexserver/llm_runtime.py:322-327); a decode step changes it only where a sequence
+ * crosses a block boundary.  This call scatters n newly granted blocks into a table that stays on
+ * the device:  tables[l][upd_row[i]][h][upd_block[i]] = upd_ids[i][l][h]  for all l, h.
+ * upd_ids rows have the [layer][head] order in which the allocator grants a logical block
+ * (csrc/batch_scheduler.h:19-20).  All pointers are device memory.
+ * ---------------------------------------------------------------------- */
+int mux_block_table_append(int32_t* tables, int64_t layer_stride, int64_t row_stride, int64_t head_stride,
+                           int32_t num_layers, int32_t num_rows, int32_t num_kv_heads, int32_t max_blocks,
+                           const int32_t* upd_row, const int32_t* upd_block, const int32_t* upd_ids,
+                           int32_t num_updates, void* cuda_stream);
 
 /* Reads and clears the device status word (MUX_DEV_* bits) of the current
  * device.  Synchronises the given stream. Returns a negative mux_status_t on failure. */

@@ -20,7 +20,7 @@ MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 class CacheWriteArgs(C.Structure):
@@ -49,6 +49,7 @@ class AttnArgs(C.Structure):
         ("block_tables", C.c_void_p),
         ("bt_seq_stride", C.c_int64), ("bt_head_stride", C.c_int64),
         ("context_lens", C.c_void_p),
+        ("seq_rows", C.c_void_p),
         ("scale", C.c_float),
         ("num_seqs", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
         ("head_size", C.c_int32), ("block_size", C.c_int32), ("max_context_len", C.c_int32),
@@ -118,6 +119,8 @@ SIGNATURES = {
     "mux_decode_attention": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_decode_attention_mixed": (C.c_int, [C.POINTER(DecodeMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_rotary_embedding": (C.c_int, [C.POINTER(RotaryArgs), C.c_void_p]),
+    "mux_block_table_append": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                         C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),
     "mux_kv_storage_create": (C.c_void_p, [C.c_int32]),
     "mux_kv_storage_destroy": (None, [C.c_void_p]),

@@ -26,6 +26,7 @@ struct AttnParams {
   const int* block_tables;
   const int* context_lens;
   const int* head_mapping;
+  const int* seq_rows;   // optional: row of each sequence in a persistent block table
   const int* item_ctx;
   const int* item_q_row;
   const int* item_group;
@@ -112,7 +113,8 @@ __device__ __forceinline__ ItemDesc load_item(const AttnParams& p, int item) {
     d.ctx = p.context_lens[d.seq];
     d.G = p.group;
     d.scale = p.scale;
-    d.bt_row = p.block_tables + (long long)d.seq * p.bt_s0 + (long long)d.kvh * p.bt_s1;
+    const long long row = p.seq_rows != nullptr ? p.seq_rows[d.seq] : d.seq;
+    d.bt_row = p.block_tables + row * p.bt_s0 + (long long)d.kvh * p.bt_s1;
   }
   return d;
 }

@@ -625,6 +625,7 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.block_tables = a->block_tables;
   prm.context_lens = a->context_lens;
   prm.head_mapping = a->head_mapping;
+  prm.seq_rows = a->seq_rows;
   prm.q_s0 = a->q_seq_stride;
   prm.q_s1 = a->q_head_stride;
   prm.o_s0 = a->out_seq_stride;

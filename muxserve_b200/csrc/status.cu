@@ -67,7 +67,7 @@ const char* mux_strerror(int status) {
 
 int mux_last_cuda_error(void) { return g_last_cuda_error; }
 
-int mux_abi_version(void) { return 4; }
+int mux_abi_version(void) { return 5; }
 
 int mux_device_status(void* cuda_stream) {
   unsigned* p = mux::device_status_ptr();

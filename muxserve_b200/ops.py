@@ -131,7 +131,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                     block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
                     max_context_len: int, *, num_kv_heads: Optional[int] = None,
                     partition_size: int = 0, num_stages: int = 0, flags: int = 0,
-                    _new_kv=None, _rope=None) -> None:
+                    seq_rows: Optional[torch.Tensor] = None, _new_kv=None, _rope=None) -> None:
     """Decode attention of one query token per sequence over the paged pool.
 
     ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
@@ -140,7 +140,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
     (muxserve/flexserver/llm_runtime.py:327) — or [S, max_blocks] when all kv
     heads share a list.  ``head_mapping``: int32 [Hq] kv head of each q head, or
     ``None`` for contiguous groups.  ``context_lens``: int32 [S], counting the
-    token written by this step's ``reshape_and_cache``.
+    token written by this step's ``reshape_and_cache``.  ``seq_rows`` (int32 [S], optional):
+    sequence ``s`` uses row ``seq_rows[s]`` of ``block_tables`` (``device_tables.DeviceBlockTables``).
     """
     _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, head_mapping=head_mapping,
                   block_tables=block_tables, context_lens=context_lens)
@@ -171,7 +172,13 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         raise ValueError("block_tables must be [S, H, max_blocks] or [S, max_blocks]")
     if num_kv_heads is not None and num_kv_heads != H:
         raise ValueError("num_kv_heads does not match block_tables")
-    if block_tables.shape[0] != S:
+    sr_ptr = None
+    if seq_rows is not None:
+        _require_cuda(seq_rows=seq_rows)
+        if seq_rows.dtype != torch.int32 or seq_rows.dim() != 1 or seq_rows.shape[0] != S or not seq_rows.is_contiguous():
+            raise ValueError("seq_rows must be a contiguous int32 [num_seqs] tensor")
+        sr_ptr = seq_rows.data_ptr()
+    elif block_tables.shape[0] != S:
         raise ValueError("block_tables and q differ in the number of sequences")
     if block_tables.shape[-1] * block_size < max_context_len:
         raise ValueError("block_tables has fewer blocks per sequence than max_context_len needs")
@@ -185,7 +192,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         out_seq_stride=o_ss, out_head_stride=o_hs,
         key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(), num_blocks=nb,
         head_mapping=hm_ptr, block_tables=block_tables.data_ptr(),
-        bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(),
+        bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(), seq_rows=sr_ptr,
         scale=float(scale), num_seqs=S, num_q_heads=Hq, num_kv_heads=H, head_size=HEAD_SIZE,
         block_size=block_size, max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
         partition_size=partition_size, num_stages=num_stages, flags=flags)

@@ -21,7 +21,7 @@ def _args(_lib, out, q, kc, vc, bt, ctx, scale, max_ctx, psize):
         key_cache=kc.data_ptr(), value_cache=vc.data_ptr(), num_blocks=kc.shape[0], head_mapping=None,
         block_tables=bt.data_ptr(), bt_seq_stride=bt.stride(0), bt_head_stride=bt.stride(1),
         context_lens=ctx.data_ptr(), scale=scale, num_seqs=S, num_q_heads=Hq, num_kv_heads=bt.shape[1],
-        head_size=128, block_size=kc.shape[2], max_context_len=max_ctx,
+        seq_rows=None, head_size=128, block_size=kc.shape[2], max_context_len=max_ctx,
         dtype=_lib.MUX_DTYPE_F16 if q.dtype == torch.float16 else _lib.MUX_DTYPE_BF16,
         partition_size=psize, num_stages=0)
 
