@@ -102,8 +102,10 @@ int mux_reshape_and_cache(const mux_cache_write_args_t* args, void* cuda_stream)
  * every (sequence, kv head) has its own block list.
  *   out[s, hq, :] = softmax_j(scale * q[s, hq, :] . K_j) . V_j ,  j < context_lens[s]
  * with kv head h = head_mapping[hq] (NULL = hq / (num_q_heads/num_kv_heads)).
- * Entries of a block list at or beyond ceil(context_len / block_size) are
- * never read (the reference leaves them uninitialised).
+ * Every block list must have ceil(max_context_len / block_size) readable
+ * entries (the width the reference gives the table); entries at or beyond
+ * ceil(context_len / block_size) may hold anything (the reference leaves them
+ * uninitialised): they are never used as block ids.
  *
  * Long contexts are split into partitions of partition_size tokens that are
  * combined through the caller's workspace (flash-decoding).  Sizes come from

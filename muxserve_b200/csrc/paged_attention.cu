@@ -48,6 +48,12 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   griddep_wait();               // inputs may be written by the previous kernel of the stream
   griddep_launch_dependents();  // the next kernel may start being scheduled behind this grid
   ItemDesc d = load_item<MIXED>(p, item);
+  // The producer warp asks for the partition's first 32 block ids at once, before the context length
+  // has arrived: entries below ceil(max_context_len / BS) exist in every block list whatever its length
+  // (unused ones may hold anything and are dropped below), so the two loads overlap.
+  int spec_id = 0;
+  if (warp == kConsumerWarps && lane < p.pb && part * p.pb + lane < (p.max_context_len + BS - 1) / BS)
+    spec_id = d.bt_row[part * p.pb + lane];
   if (d.ctx < 0 || d.ctx > p.max_context_len) {
     if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
     d.ctx = d.ctx < 0 ? 0 : p.max_context_len;
@@ -88,7 +94,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     // ---------------- producer warp ----------------
     int* ids = reinterpret_cast<int*>(smem + L.ids);
     for (int i = lane; i < nblk; i += 32) {
-      int id = d.bt_row[part * p.pb + i];
+      int id = i < 32 ? spec_id : d.bt_row[part * p.pb + i];
       if (id < 0 || id >= p.num_blocks) {
         atomicOr(p.status, MUX_DEV_BAD_BLOCK_ID);
         id = -1;  // block 0 is read in its place; nothing is ever written through it
@@ -354,15 +360,23 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
   const int geff = info.geff;
   T* out = static_cast<T*>(p.out);
   const long long slot0 = ((long long)item * p.head_tiles + htile) * p.max_parts;
+  const int lane = tid & 31;
   for (int n = 0; n < geff; ++n) {
+    // every warp reduces (max, sum) over the partitions with its lanes, so the loads go out together
     float M = -INFINITY;
-    for (int k = 0; k < nparts; ++k) M = fmaxf(M, p.ws_ml[((slot0 + k) * p.gs + n) * 2]);
-    float acc = 0.f, lsum = 0.f;
+    for (int k = lane; k < nparts; k += 32) M = fmaxf(M, p.ws_ml[((slot0 + k) * p.gs + n) * 2]);
+    M = warp_max(M);
+    float lsum = 0.f;
+    for (int k = lane; k < nparts; k += 32) {
+      const long long r = (slot0 + k) * p.gs + n;
+      lsum += p.ws_ml[r * 2 + 1] * __expf(p.ws_ml[r * 2] - M);
+    }
+    lsum = warp_sum(lsum);
+    float acc = 0.f;
+#pragma unroll 4
     for (int k = 0; k < nparts; ++k) {
       const long long r = (slot0 + k) * p.gs + n;
-      const float w = __expf(p.ws_ml[r * 2] - M);
-      lsum += p.ws_ml[r * 2 + 1] * w;
-      acc += p.ws_acc[r * kHeadSize + tid] * w;
+      acc += p.ws_acc[r * kHeadSize + tid] * __expf(p.ws_ml[r * 2] - M);
     }
     out[info.ooff[n] + tid] = from_float<T>(acc / lsum);
   }
