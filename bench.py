@@ -347,8 +347,15 @@ def run_native(args):
     gpu_launches = ops.launch_count - launches0 if graph is None else per_step_launches * args.steps
     barrier()
     clocks = sampler.stop()
+    ms_local = e0.elapsed_time(e1) / args.steps
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
+    ms_ranks = [ms_local]
+    if world > 1:          # every rank's own time, to tell a slow GPU from a slow path
+        t = torch.tensor([ms_local], dtype=torch.float64, device=dev)
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        ms_ranks = [float(g.item()) for g in gathered]
     if graph is not None:
         # the kernel-level span cannot be bracketed inside a graph: a second, eager pass of the same
         # steps with CUDA events around every attention launch gives it
@@ -539,7 +546,7 @@ def run_native(args):
                          "eager_span_ms": eager_span_ms},
             "step": ("decode_attention per layer (cache write fused into the attention launch)" if fused else
                      "reshape_and_cache + paged_attention per layer"),
-            "eager_ms_per_step": ms_eager,
+            "eager_ms_per_step": ms_eager, "ms_per_step_by_rank": ms_ranks,
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
             "clocks": clocks, "device_status": status,
         }
