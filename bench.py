@@ -269,7 +269,9 @@ def run_native(args):
     kc, vc = flexstore.allocate_gpu_cache(num_blocks, BLOCK, dt, dev)
     workloads.fill_pool_(kc, vc, args.seed + 17 * rank)
 
-    gen = torch.Generator().manual_seed(args.seed + 1000 * rank)
+    # every replica gets the same context lengths (the same work per GPU, which is what weak scaling
+    # compares); pool contents, block scatter and q/k/v differ by rank
+    gen = torch.Generator().manual_seed(args.seed)
     ctx = workloads.uniform_context_lens(S, w["lo"], w["hi"], gen)
     per_layer = workloads.blocks_needed(ctx, 1, H, BLOCK)
     L_res = max(1, min(L, int(num_blocks * 0.98) // per_layer))     # distinct resident layers
