@@ -283,6 +283,10 @@ int mux_block_table_append(int32_t* tables, int64_t layer_stride, int64_t row_st
                            const int32_t* upd_row, const int32_t* upd_block, const int32_t* upd_ids,
                            int32_t num_updates, void* cuda_stream);
 
+/* Self-test of the failure path: launches one warp that waits, with the same bounded wait the
+ * kernels use, on a barrier nothing completes.  The wait gives up after a (shortened) poll limit, well under a second, sets MUX_DEV_WAIT_TIMEOUT and the kernel ends normally: the context stays usable. */
+int mux_selftest_wait_timeout(void* cuda_stream);
+
 /* Reads and clears the device status word (MUX_DEV_* bits) of the current
  * device.  Synchronises the given stream. Returns a negative mux_status_t on failure. */
 int mux_device_status(void* cuda_stream);

@@ -121,6 +121,7 @@ SIGNATURES = {
     "mux_rotary_embedding": (C.c_int, [C.POINTER(RotaryArgs), C.c_void_p]),
     "mux_block_table_append": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "mux_selftest_wait_timeout": (C.c_int, [C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),
     "mux_kv_storage_create": (C.c_void_p, [C.c_int32]),
     "mux_kv_storage_destroy": (None, [C.c_void_p]),

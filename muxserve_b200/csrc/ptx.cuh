@@ -59,8 +59,8 @@ constexpr uint32_t kWaitLimit = 1u << 20;
 constexpr uint32_t kWaitRecheck = 1u << 10;
 
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, unsigned* status,
-                                          unsigned timeout_bit) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                                          unsigned timeout_bit, uint32_t limit = kWaitLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return;
     if ((i & (kWaitRecheck - 1)) == kWaitRecheck - 1 &&
         (*reinterpret_cast<volatile unsigned*>(status) & timeout_bit))

@@ -2,6 +2,7 @@
 #include <mutex>
 
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace {
 
@@ -11,6 +12,18 @@ constexpr int kMaxDevices = 64;
 unsigned* g_status_ptr[kMaxDevices] = {};
 std::mutex g_status_mutex;
 thread_local int g_last_cuda_error = 0;
+
+// One warp waits, with the library's bounded wait, on a barrier that nothing will ever complete.
+__global__ void wait_selftest_kernel(unsigned* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t b = mux::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mux::mbar_init(b, 1);
+    mux::mbar_init_fence();
+  }
+  __syncwarp();
+  mux::mbar_wait(b, 0, status, MUX_DEV_WAIT_TIMEOUT, 1u << 16);  // same wait, a 16th of the poll limit
+}
 
 }  // namespace
 
@@ -68,6 +81,14 @@ const char* mux_strerror(int status) {
 int mux_last_cuda_error(void) { return g_last_cuda_error; }
 
 int mux_abi_version(void) { return 5; }
+
+int mux_selftest_wait_timeout(void* cuda_stream) {
+  unsigned* p = mux::device_status_ptr();
+  if (p == nullptr) return MUX_ERR_CUDA;
+  wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? MUX_OK : mux::record_cuda_error(e);
+}
 
 int mux_device_status(void* cuda_stream) {
   unsigned* p = mux::device_status_ptr();

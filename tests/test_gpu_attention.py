@@ -273,3 +273,20 @@ def test_attention_max_context_8192_gqa(env):
                             case.max_context_len, partition_size=psize)
         _, _, ref = gu.oracle_step(case, kc, vc)
         gu.assert_close(out, ref, f"ctx 8200 partition {psize}")
+
+
+def test_bounded_wait_runs_out_and_is_reported(env, built_lib):
+    """A wait that nothing satisfies ends by itself: status bit set, kernel returns, later launches work."""
+    import time
+    ops, gu = env
+    from muxserve_b200 import _lib
+    assert ops.device_status() == 0
+    t0 = time.perf_counter()
+    assert built_lib.mux_selftest_wait_timeout(torch.cuda.current_stream().cuda_stream) == 0
+    assert ops.device_status() == _lib.MUX_DEV_WAIT_TIMEOUT        # synchronises: the kernel has ended
+    assert time.perf_counter() - t0 < 5.0
+    case, kc, vc = gu.make_case(2, 2, 2, [40, 700], 16, torch.float16, seed=1, num_blocks=256)
+    out = run(ops, gu, case, kc, vc)
+    _, _, ref = gu.oracle_step(case, kc, vc)
+    gu.assert_close(out, ref, "after a timed-out wait")
+    assert ops.device_status() == 0
