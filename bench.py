@@ -329,13 +329,20 @@ def run_native(args):
     sampler = ClockSampler(local_rank)
     graph = None
     if not args.eager:
-        torch.cuda.synchronize()
-        l0 = ops.launch_count
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        per_step_launches = ops.launch_count - l0
-        graph.replay()
+        try:
+            torch.cuda.synchronize()
+            l0 = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            per_step_launches = ops.launch_count - l0
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:      # capture refused: time the Python-issued launches instead
+            print(f"bench: CUDA graph capture failed ({type(exc).__name__}: {exc}); timing eager launches",
+                  file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
     barrier()
     sampler.start()
     launches0 = ops.launch_count
@@ -383,13 +390,17 @@ def run_native(args):
         for _ in range(3):
             step(fuse=False)
         run2 = lambda: step(fuse=False)
-        if not args.eager:
-            torch.cuda.synchronize()
-            g2 = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g2):
-                step(fuse=False)
-            run2 = g2.replay
-            run2()
+        if graph is not None:
+            try:
+                torch.cuda.synchronize()
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2):
+                    step(fuse=False)
+                g2.replay()
+                torch.cuda.synchronize()
+                run2 = g2.replay
+            except Exception:
+                torch.cuda.synchronize()
         barrier()
         e0.record()
         for _ in range(args.steps):
@@ -643,13 +654,20 @@ def run_native_c3(args):
     sampler = ClockSampler(local_rank)
     graph = None
     if not args.eager:
-        torch.cuda.synchronize()
-        l0 = ops.launch_count
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        per_step_launches = ops.launch_count - l0
-        graph.replay()
+        try:
+            torch.cuda.synchronize()
+            l0 = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            per_step_launches = ops.launch_count - l0
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:      # capture refused: time the Python-issued launches instead
+            print(f"bench: CUDA graph capture failed ({type(exc).__name__}: {exc}); timing eager launches",
+                  file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
     barrier()
     sampler.start()
     launches0 = ops.launch_count
