@@ -1,0 +1,52 @@
+"""CPU checks of the host-side helpers around the kernels: workload generators and the row / grant
+bookkeeping of the persistent device tables (no GPU: the table itself is a CPU tensor here)."""
+import numpy as np
+import torch
+
+from muxserve_b200 import workloads
+from muxserve_b200.device_tables import DeviceBlockTables
+
+
+def test_scatter_block_tables_never_shares_a_block():
+    gen = torch.Generator().manual_seed(0)
+    ctx = workloads.lognormal_context_lens(20, 256, 1.0, 16, 4096, gen)
+    assert int(ctx.min()) >= 16 and int(ctx.max()) <= 4096
+    need = workloads.blocks_needed(ctx, 3, 5, 16)
+    perm = torch.randperm(need + 50, generator=gen)
+    bt, nxt = workloads.scatter_block_tables(ctx, 3, 5, 16, perm)
+    used = bt[bt >= 0]
+    assert used.numel() == need == nxt and used.unique().numel() == need
+    for s in range(20):
+        nb = (int(ctx[s]) + 15) // 16
+        assert (bt[:, s, :, :nb] >= 0).all() and (bt[:, s, :, nb:] == -1).all()
+    slots = workloads.last_token_slots(bt, ctx, 16, new_tokens=3)
+    assert slots.shape == (60, 3, 5)
+    s, j = 7, 2                                           # last of the three new tokens of sequence 7
+    pos = int(ctx[s]) - 1
+    assert int(slots[s * 3 + j, 1, 4]) == int(bt[1, s, 4, pos // 16]) * 16 + pos % 16
+
+
+def test_device_tables_bookkeeping():
+    t = DeviceBlockTables(num_layers=2, num_kv_heads=3, max_rows=3, max_blocks=4, device="cpu")
+    LH = 6
+    # prefill grant: request 7 gets 2 blocks, request 9 gets 1; request 5 was preempted by the allocator
+    req = np.array([7, 2, 0, 9, 1, 0, 5, 1, 0], dtype=np.int32)
+    info = np.concatenate([[2], np.arange(100, 100 + 3 * LH)]).astype(np.int32)
+    t.stage_grant(req, info)
+    assert t.row_of == {7: 0, 9: 1} and t.blocks_of == {7: 2, 9: 1}
+    assert t._rows == [0, 0, 1] and t._blks == [0, 1, 0]
+    ids = np.concatenate(t._ids, axis=0)
+    assert ids.shape == (3, LH) and ids[1].tolist() == list(range(106, 112)) and ids[2].tolist() == list(range(112, 118))
+    # decode step without a boundary crossing stages nothing; one with a crossing appends at the next block
+    t._rows, t._blks, t._ids = [], [], []
+    t.stage_grant(np.array([7, 0, 1, 9, 1, 1], dtype=np.int32), np.concatenate([[2], np.arange(6)]).astype(np.int32))
+    assert t._rows == [1] and t._blks == [1] and t.blocks_of[9] == 2
+    # rows are recycled
+    t.release([7])
+    assert t.assign(11) == 0 and t.blocks_of[11] == 0
+    t.assign(12)
+    try:
+        t.assign(13)
+        raise AssertionError("expected the table to be full")
+    except RuntimeError:
+        pass
