@@ -34,6 +34,12 @@ cache_write_kernel(const __grid_constant__ CacheWriteParams p) {
   if (row >= (long long)p.num_tokens * p.num_heads) return;
   const int t = (int)(row / p.num_heads);
   const int h = (int)(row - (long long)t * p.num_heads);
+  // the row's data and its slot are independent loads: issue all of them before the first use
+  const T* krow = static_cast<const T*>(p.k) + t * p.k_ts + h * p.k_hs;
+  const T* vrow = static_cast<const T*>(p.v) + t * p.v_ts + h * p.v_hs;
+  const uint2 vval = *reinterpret_cast<const uint2*>(vrow + 4 * lane);
+  uint4 kval = make_uint4(0u, 0u, 0u, 0u);
+  if (lane < 16) kval = *reinterpret_cast<const uint4*>(krow + 8 * lane);
   const long long slot = p.slots[t * p.s_ts + h * p.s_hs];
   if (slot < 0) return;  // padding row
   const long long b = slot / BS;
@@ -42,24 +48,18 @@ cache_write_kernel(const __grid_constant__ CacheWriteParams p) {
     if (lane == 0) atomicOr(p.status, MUX_DEV_BAD_SLOT);
     return;
   }
-  const T* krow = static_cast<const T*>(p.k) + t * p.k_ts + h * p.k_hs;
-  const T* vrow = static_cast<const T*>(p.v) + t * p.v_ts + h * p.v_hs;
   T* kblk = static_cast<T*>(p.kc) + b * (128 * BS);
   T* vblk = static_cast<T*>(p.vc) + b * (128 * BS);
-  // V first (all lanes): lane owns d = 4*lane .. 4*lane+3
+  // V (all lanes): lane owns d = 4*lane .. 4*lane+3
   {
-    const uint2 val = *reinterpret_cast<const uint2*>(vrow + 4 * lane);
     unsigned short* dst = reinterpret_cast<unsigned short*>(vblk) + (4 * lane) * BS + o;
-    dst[0] = (unsigned short)(val.x & 0xffffu);
-    dst[BS] = (unsigned short)(val.x >> 16);
-    dst[2 * BS] = (unsigned short)(val.y & 0xffffu);
-    dst[3 * BS] = (unsigned short)(val.y >> 16);
+    dst[0] = (unsigned short)(vval.x & 0xffffu);
+    dst[BS] = (unsigned short)(vval.x >> 16);
+    dst[2 * BS] = (unsigned short)(vval.y & 0xffffu);
+    dst[3 * BS] = (unsigned short)(vval.y >> 16);
   }
   // K: lanes 0..15 own one 8-wide chunk each
-  if (lane < 16) {
-    const uint4 val = *reinterpret_cast<const uint4*>(krow + 8 * lane);
-    *reinterpret_cast<uint4*>(kblk + lane * (BS * 8) + o * 8) = val;
-  }
+  if (lane < 16) *reinterpret_cast<uint4*>(kblk + lane * (BS * 8) + o * 8) = kval;
 }
 
 template <typename T>
