@@ -124,13 +124,12 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   float* S = reinterpret_cast<float*>(smem + L.s);
   const int SROW = L.srow;
 
-  // FUSE: the warp that will consume the block holding the new token fetches the new rows now.
+  // FUSE: the warp that consumes the block holding the new token also appends it (the new rows are
+  // fetched only there, so that they do not occupy registers through the main loops).
   const int new_local = d.ctx - 1 - tok0;  // the appended token's index inside this partition
   const int jl = new_local / BS, ol = new_local % BS;
   const bool appends = FUSE && part == nparts - 1 && (jl & (kConsumerWarps - 1)) == warp;
   const int* ids_c = reinterpret_cast<const int*>(smem + L.ids);
-  uint4 knew = make_uint4(0u, 0u, 0u, 0u);
-  uint2 vnew = make_uint2(0u, 0u);
   // Rotary embedding of the decode step: the query and the new key sit at position ctx - 1.
   const T* rope_row = nullptr;
   if (FUSE && p.rope_cache != nullptr) {
@@ -141,14 +140,6 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     }
     rope_row = static_cast<const T*>(p.rope_cache) + pos * kHeadSize;
   }
-  if (appends) {
-    const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
-    const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
-    if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
-    vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
-    if (rope_row != nullptr) knew = rope_row16<T>(knew, lane, rope_row);  // rotary at position ctx - 1
-  }
-
   // q as the B operand (k = d, n = head): b0 = q[g][16ks + 2tq, +1], b1 = q[g][16ks + 8 + 2tq, +1]
   uint32_t qf[8][2];
   {
@@ -185,6 +176,11 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       const uint32_t tile = ring + stage * TILE;
       if (FUSE && appends && jb == jl) {  // K row of the new token: 16 pieces of 16 bytes
+        const long long ko = MIXED ? (long long)item * p.kn_s0
+                                   : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
+        uint4 knew = make_uint4(0u, 0u, 0u, 0u);
+        if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
+        if (rope_row != nullptr) knew = rope_row16<T>(knew, lane, rope_row);  // rotary at position ctx - 1
         if (lane < 16) {
           const uint32_t off = lane * CHUNK + ol * 16;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile + off), "r"(knew.x), "r"(knew.y),
@@ -254,6 +250,9 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       const uint32_t tile = ring + stage * TILE;
       if (FUSE && appends && jb == jl) {  // V column of the new token: 128 single elements
+        const long long vo = MIXED ? (long long)item * p.vn_s0
+                                   : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
+        const uint2 vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
         const unsigned short e[4] = {(unsigned short)(vnew.x & 0xffffu), (unsigned short)(vnew.x >> 16),
                                      (unsigned short)(vnew.y & 0xffffu), (unsigned short)(vnew.y >> 16)};
         unsigned short* gdst = reinterpret_cast<unsigned short*>(
