@@ -55,7 +55,7 @@ struct AttnParams {
 
 // Shared-memory carve-up, identical on host (sizing) and device.
 struct SmemLayout {
-  int ring, s, ids, info, bars, total;
+  int ring, s, ids, newrows, info, bars, total;
   int srow;
 };
 
@@ -75,6 +75,8 @@ __host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs
   L.ids = off;
   off += pb * 4;
   off = (off + 15) & ~15;
+  L.newrows = off;   // fused decode step: the new K row (256 B) and V row (256 B), staged by the producer warp
+  off += 512;
   L.info = off;
   off += 8 * 8 + 8 * 8 + 8 * 2 * 4 + 16;  // qoff, ooff, ml, geff
   L.bars = off;

@@ -101,6 +101,22 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       }
       ids[i] = id;
     }
+    if (FUSE && part == nparts - 1) {
+      // The decode step's new K/V rows of this item go to shared memory now (rotary applied to K),
+      // long before the consumer warp that appends them needs them.
+      const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
+      const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
+      uint4 knew = make_uint4(0u, 0u, 0u, 0u);
+      if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
+      const uint2 vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
+      if (p.rope_cache != nullptr) {
+        long long pos = min((long long)d.ctx - 1, p.rope_max_position - 1);
+        knew = rope_row16<T>(knew, lane, static_cast<const T*>(p.rope_cache) + pos * kHeadSize);
+      }
+      unsigned char* nr = smem + L.newrows;
+      if (lane < 16) *reinterpret_cast<uint4*>(nr + 16 * lane) = knew;
+      *reinterpret_cast<uint2*>(nr + 256 + 8 * lane) = vnew;
+    }
     __syncwarp();
     if (lane == 0) {
       const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
@@ -124,8 +140,8 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   float* S = reinterpret_cast<float*>(smem + L.s);
   const int SROW = L.srow;
 
-  // FUSE: the warp that consumes the block holding the new token also appends it (the new rows are
-  // fetched only there, so that they do not occupy registers through the main loops).
+  // FUSE: the warp that consumes the block holding the new token also appends it (the producer warp
+  // has staged the new rows in shared memory by then).
   const int new_local = d.ctx - 1 - tok0;  // the appended token's index inside this partition
   const int jl = new_local / BS, ol = new_local % BS;
   const bool appends = FUSE && part == nparts - 1 && (jl & (kConsumerWarps - 1)) == warp;
@@ -176,12 +192,8 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       const uint32_t tile = ring + stage * TILE;
       if (FUSE && appends && jb == jl) {  // K row of the new token: 16 pieces of 16 bytes
-        const long long ko = MIXED ? (long long)item * p.kn_s0
-                                   : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
-        uint4 knew = make_uint4(0u, 0u, 0u, 0u);
-        if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
-        if (rope_row != nullptr) knew = rope_row16<T>(knew, lane, rope_row);  // rotary at position ctx - 1
         if (lane < 16) {
+          const uint4 knew = *reinterpret_cast<const uint4*>(smem + L.newrows + 16 * lane);
           const uint32_t off = lane * CHUNK + ol * 16;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(tile + off), "r"(knew.x), "r"(knew.y),
                        "r"(knew.z), "r"(knew.w) : "memory");
@@ -250,9 +262,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       const uint32_t tile = ring + stage * TILE;
       if (FUSE && appends && jb == jl) {  // V column of the new token: 128 single elements
-        const long long vo = MIXED ? (long long)item * p.vn_s0
-                                   : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
-        const uint2 vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
+        const uint2 vnew = *reinterpret_cast<const uint2*>(smem + L.newrows + 256 + 8 * lane);
         const unsigned short e[4] = {(unsigned short)(vnew.x & 0xffffu), (unsigned short)(vnew.x >> 16),
                                      (unsigned short)(vnew.y & 0xffffu), (unsigned short)(vnew.y >> 16)};
         unsigned short* gdst = reinterpret_cast<unsigned short*>(
