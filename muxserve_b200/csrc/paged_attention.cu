@@ -54,6 +54,16 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   int spec_id = 0;
   if (warp == kConsumerWarps && lane < p.pb && part * p.pb + lane < (p.max_context_len + BS - 1) / BS)
     spec_id = d.bt_row[part * p.pb + lane];
+  // FUSE: the item's new K/V rows are requested at the same time (by every partition's producer warp;
+  // only the last partition uses them), so that no load latency is left when they are needed.
+  uint4 knew = make_uint4(0u, 0u, 0u, 0u);
+  uint2 vnew = make_uint2(0u, 0u);
+  if (FUSE && warp == kConsumerWarps) {
+    const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
+    const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
+    if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
+    vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
+  }
   if (d.ctx < 0 || d.ctx > p.max_context_len) {
     if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
     d.ctx = d.ctx < 0 ? 0 : p.max_context_len;
@@ -104,11 +114,6 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     if (FUSE && part == nparts - 1) {
       // The decode step's new K/V rows of this item go to shared memory now (rotary applied to K),
       // long before the consumer warp that appends them needs them.
-      const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
-      const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
-      uint4 knew = make_uint4(0u, 0u, 0u, 0u);
-      if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
-      const uint2 vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
       if (p.rope_cache != nullptr) {
         long long pos = min((long long)d.ctx - 1, p.rope_max_position - 1);
         knew = rope_row16<T>(knew, lane, static_cast<const T*>(p.rope_cache) + pos * kHeadSize);
