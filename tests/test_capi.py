@@ -93,3 +93,15 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libmuxb200.so")
     with pytest.raises(ImportError, match="no CPU fallback"):
         _lib.lib()
+
+
+def test_plain_c_client_links_and_runs(built_lib, tmp_path):
+    """The header compiles as C and a C program can drive the host side of the library."""
+    import subprocess
+    from muxserve_b200 import _lib
+    exe = tmp_path / "abi_host"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(ROOT / "tests" / "c" / "abi_host.c"),
+                    "-o", str(exe), f"-L{_lib.LIB_PATH.parent}", "-lmuxb200", f"-Wl,-rpath,{_lib.LIB_PATH.parent}"],
+                   check=True, capture_output=True, text=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and "c abi ok" in out.stdout, out.stdout + out.stderr
