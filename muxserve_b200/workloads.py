@@ -86,10 +86,10 @@ def scatter_block_tables(context_lens: torch.Tensor, num_layers: int, num_kv_hea
     for s in range(S):
         n = int(nblk[s])
         cnt = num_layers * num_kv_heads * n
+        if off + cnt > block_ids.numel():
+            raise ValueError("pool too small for this workload")
         tables[:, s, :, :n] = block_ids[off:off + cnt].view(num_layers, num_kv_heads, n).to(torch.int32)
         off += cnt
-    if off > block_ids.numel():
-        raise ValueError("pool too small for this workload")
     return tables, off
 
 
