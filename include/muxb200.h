@@ -270,6 +270,39 @@ typedef struct {
 int mux_rotary_embedding(const mux_rotary_args_t* args, void* cuda_stream);
 
 /* ------------------------------------------------------------------------
+ * prompt-phase attention — causal self-attention of every prompt over its own tokens, the step
+ * PagedAttentionWithRoPE runs on the prompt rows of a batch (muxserve/flexserver/models/llama.py:160-161,
+ * prompt lengths from input_metadata.prompt_lens, muxserve/flexserver/llm_runtime.py:298-330) before
+ * their K/V rows go to the pool through mux_reshape_and_cache with the slots of
+ * csrc/batch_scheduler.h:42-56.  The rows of all prompts are concatenated:
+ * prompt i owns rows cu_seqlens[i] .. cu_seqlens[i+1]-1, row t attends to rows <= t of its own prompt.
+ * q head h reads kv head h / (num_q_heads / num_kv_heads).  Runs on tcgen05 tensor cores (TMA-staged
+ * 128 x 128 tiles, accumulators in tensor memory).  No workspace.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  void* out;                 /* [total_tokens, num_q_heads, 128] */
+  const void* q;             /* [total_tokens, num_q_heads, 128] */
+  const void* k;             /* [total_tokens, num_kv_heads, 128] */
+  const void* v;
+  int64_t out_seq_stride, out_head_stride;   /* elements; multiples of 8, innermost dimension contiguous */
+  int64_t q_seq_stride, q_head_stride;
+  int64_t k_seq_stride, k_head_stride;
+  int64_t v_seq_stride, v_head_stride;
+  const int32_t* cu_seqlens; /* device, [num_seqs + 1], cu_seqlens[0] = 0, non-decreasing */
+  float scale;               /* > 0 */
+  int32_t num_seqs;
+  int32_t total_tokens;      /* rows of q / k / v / out */
+  int32_t max_prompt_len;    /* host-known upper bound of every prompt length (sizes the grid) */
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_size;
+  int32_t dtype;
+  int32_t reserved;
+} mux_prefill_args_t;
+
+int mux_prefill_attention(const mux_prefill_args_t* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------
  * Persistent block tables on the device.  The reference rebuilds and uploads the whole
  * [L, S, H, max_blocks] table every step (csrc/batch_scheduler.cpp:156-169,
  * muxserve/flexserver/llm_runtime.py:322-327); a decode step changes it only where a sequence

@@ -20,7 +20,7 @@ MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 class CacheWriteArgs(C.Structure):
@@ -102,6 +102,20 @@ class RotaryArgs(C.Structure):
     ]
 
 
+class PrefillArgs(C.Structure):
+    _fields_ = [
+        ("out", C.c_void_p), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("out_seq_stride", C.c_int64), ("out_head_stride", C.c_int64),
+        ("q_seq_stride", C.c_int64), ("q_head_stride", C.c_int64),
+        ("k_seq_stride", C.c_int64), ("k_head_stride", C.c_int64),
+        ("v_seq_stride", C.c_int64), ("v_head_stride", C.c_int64),
+        ("cu_seqlens", C.c_void_p), ("scale", C.c_float),
+        ("num_seqs", C.c_int32), ("total_tokens", C.c_int32), ("max_prompt_len", C.c_int32),
+        ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_size", C.c_int32),
+        ("dtype", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 _I32P = C.POINTER(C.c_int32)
 _I64P = C.POINTER(C.c_int64)
 
@@ -119,6 +133,7 @@ SIGNATURES = {
     "mux_decode_attention": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_decode_attention_mixed": (C.c_int, [C.POINTER(DecodeMixedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mux_rotary_embedding": (C.c_int, [C.POINTER(RotaryArgs), C.c_void_p]),
+    "mux_prefill_attention": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
     "mux_block_table_append": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "mux_selftest_wait_timeout": (C.c_int, [C.c_void_p]),

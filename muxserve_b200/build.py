@@ -19,7 +19,8 @@ CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libmuxb200.so"
 BUILD_DIR = PKG_DIR / "build"
 
-CUDA_SOURCES = ["status.cu", "cache_write.cu", "rotary.cu", "block_table.cu", "paged_attention.cu"]
+CUDA_SOURCES = ["status.cu", "cache_write.cu", "rotary.cu", "block_table.cu", "paged_attention.cu",
+                "prefill_attention.cu"]
 HOST_SOURCES = ["host/kv_storage.cpp", "host/batch_scheduler.cpp"]
 HEADERS = ["ptx.cuh", "internal.h", "attn_common.cuh", "rope.cuh", "../../include/muxb200.h"]
 

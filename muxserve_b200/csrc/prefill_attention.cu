@@ -1,0 +1,538 @@
+// Prompt-phase (prefill) attention: causal self-attention of every prompt of a batch over its
+// own tokens, the step PagedAttentionWithRoPE runs for the prompt rows of a batch before their
+// K/V are written to the pool (muxserve/flexserver/models/llama.py:160-161 with
+// input_metadata.prompt_lens from muxserve/flexserver/llm_runtime.py:298-330).
+//
+// This is the one GEMM-shaped kernel of the library, so it runs on the 5th-generation tensor
+// cores: one CTA owns 128 query rows of one (prompt, q head) and walks the key/value tiles of
+// 128 tokens up to the diagonal.
+//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles through 2-stage rings
+//                      (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers)
+//   warp 5 (one lane)  issues tcgen05.mma: S = Q.K^T into one of two TMEM buffers, O += P.V
+//                      into a third; tcgen05.commit signals the mbarriers
+//   warps 0-3          one thread per query row: tcgen05.ld of the S row, scale, causal mask,
+//                      online softmax (lazy rescaling of O), P written to shared memory in the
+//                      MMA's K-major swizzled layout, final O / l written to global memory
+// bf16 rounds P to 8 bits, which breaks the 2e-3 tolerance on short prompts with cancelling
+// values; there P is split into hi + lo parts and P.V takes two MMAs per step.
+// Every wait is bounded (ptx.cuh); TMEM is freed on every path that allocated it.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <type_traits>
+
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace mux {
+namespace prefill {
+
+constexpr int kTile = 128;                   // query rows per CTA = tokens per K/V tile
+constexpr int kSlabBytes = kTile * 128;      // 128 rows x 64 elements: one 128-byte-swizzled slab
+constexpr int kTileBytes = 2 * kSlabBytes;   // head size 128 = two slabs
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;          // S0 | S1 | O (3 x 128 fp32 columns), power of two
+constexpr float kRescaleStep = 8.f;          // O is rescaled only when the running max grows by 2^8
+
+enum Bar {
+  Q_FULL = 0,
+  K_FULL = 1,   // +stage
+  K_EMPTY = 3,
+  V_FULL = 5,
+  V_EMPTY = 7,
+  S_FULL = 9,   // +buffer
+  S_EMPTY = 11,
+  P_FULL = 13,
+  PV_DONE = 14,
+  NUM_BARS = 15
+};
+
+struct Params {
+  void* out;
+  int64_t out_seq_stride, out_head_stride;  // elements
+  const int32_t* cu_seqlens;                // [num_seqs + 1]
+ int total_tokens;
+  int max_prompt_len;
+  int group;                                // q heads per kv head
+  float scale_log2;                         // scale * log2(e)
+  unsigned* status;
+};
+
+template <bool SPLIT>
+constexpr int smem_bytes() {
+  // Q + 2 K + 2 V + P (hi [+ lo]) + barriers, plus slack for the 1024-byte alignment
+  return kTileBytes * (5 + (SPLIT ? 2 : 1)) + 256 + 1024;
+}
+
+// ---- tcgen05 / TMA building blocks -----------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// All earlier tcgen05.mma of this thread arrive on `bar` when they complete.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], 128 x 128 x 16, 16-bit operands, fp32 accumulate.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets
+// (all in 16-byte units), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulator, a/b format (0 f16, 1 bf16), B major (0 K, 1 MN), N = 128, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+#define MUX_F4(a, i) "=f"(a[i]), "=f"(a[i + 1]), "=f"(a[i + 2]), "=f"(a[i + 3])
+#define MUX_F4I(a, i) "f"(a[i]), "f"(a[i + 1]), "f"(a[i + 2]), "f"(a[i + 3])
+
+// This warp's 32 TMEM lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane = row).
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&s)[N]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : MUX_F4(s, OFF), MUX_F4(s, OFF + 4), MUX_F4(s, OFF + 8), MUX_F4(s, OFF + 12), MUX_F4(s, OFF + 16),
+        MUX_F4(s, OFF + 20), MUX_F4(s, OFF + 24), MUX_F4(s, OFF + 28)
+      : "r"(taddr)
+      : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&s)[N]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+      ::MUX_F4I(s, 0), MUX_F4I(s, 4), MUX_F4I(s, 8), MUX_F4I(s, 12), MUX_F4I(s, 16), MUX_F4I(s, 20),
+        MUX_F4I(s, 24), MUX_F4I(s, 28), "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+
+template <typename T, bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
+                    const __grid_constant__ CUtensorMap tmv, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // the tiles with the most work start first
+
+  griddep_wait();
+  const int start = p.cu_seqlens[seq];
+  const int len = p.cu_seqlens[seq + 1] - start;
+  if (start < 0 || len < 0 || len > p.max_prompt_len || start + len > p.total_tokens) {
+    if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);  // nothing of this prompt is read or written
+    return;
+  }
+  if (qt * kTile >= len) return;
+  const int n = qt + 1;  // key/value tiles 0..qt; the last one is the diagonal
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
+  const uint32_t sQ = base;
+  const uint32_t sK = sQ + kTileBytes;
+  const uint32_t sV = sK + 2 * kTileBytes;
+  const uint32_t sP = sV + 2 * kTileBytes;
+  const uint32_t sBar = sP + (SPLIT ? 2 : 1) * kTileBytes;
+  auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
+  const uint32_t sSlot = sBar + 8u * NUM_BARS;
+  volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sSlot - raw));
+
+  if (tid == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(K_FULL + i), 1);
+      mbar_init(bar(K_EMPTY + i), 1);
+      mbar_init(bar(V_FULL + i), 1);
+      mbar_init(bar(V_EMPTY + i), 1);
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(S_EMPTY + i), kSoftmaxThreads);
+    }
+    mbar_init(bar(P_FULL), kSoftmaxThreads);
+    mbar_init(bar(PV_DONE), 1);
+    mbar_init_fence();
+  }
+  if (warp == 5) tmem_alloc(sSlot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *slot;
+  griddep_launch_dependents();
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const int kvh = head / p.group;
+      const int q0 = start + qt * kTile;
+      mbar_arrive_expect_tx(bar(Q_FULL), kTileBytes);
+      tma_load_3d(sQ, &tmq, 0, head, q0, bar(Q_FULL));
+      tma_load_3d(sQ + kSlabBytes, &tmq, 64, head, q0, bar(Q_FULL));
+      for (int j = 0; j < n; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        const int t0 = start + j * kTile;
+        mbar_wait(bar(K_EMPTY + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_arrive_expect_tx(bar(K_FULL + st), kTileBytes);
+        tma_load_3d(sK + st * kTileBytes, &tmk, 0, kvh, t0, bar(K_FULL + st));
+        tma_load_3d(sK + st * kTileBytes + kSlabBytes, &tmk, 64, kvh, t0, bar(K_FULL + st));
+        mbar_wait(bar(V_EMPTY + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_arrive_expect_tx(bar(V_FULL + st), kTileBytes);
+        tma_load_3d(sV + st * kTileBytes, &tmv, 0, kvh, t0, bar(V_FULL + st));
+        tma_load_3d(sV + st * kTileBytes + kSlabBytes, &tmv, 64, kvh, t0, bar(V_FULL + st));
+      }
+      // No copy of this CTA may still be in flight when it ends (matters only after a failed wait).
+      for (int j = (n > 2 ? n - 2 : 0); j < n; ++j) {
+        mbar_wait(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t idesc_qk = instr_desc(fmt, 0);  // S = Q K^T: both operands K-major (d contiguous)
+      constexpr uint32_t idesc_pv = instr_desc(fmt, 1);  // O = P V: V is MN-major (d contiguous, tokens = K)
+      const uint32_t tS = tmem, tO = tmem + 256;
+      // K-major slab: rows 128 B apart, 8-row groups 1024 B apart; a 16-element k-step is 32 B inside the
+      // swizzled row, the second 64-element slab 16 KiB further.
+      auto koff = [](int ks) { return (uint64_t)((ks >> 2) * (kSlabBytes >> 4) + (ks & 3) * 2); };
+      const uint64_t dQ = smem_desc(sQ, 16, 1024);
+      const uint64_t dP = smem_desc(sP, 16, 1024);
+      mbar_wait(bar(Q_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
+      auto issue_qk = [&](int j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        mbar_wait(bar(K_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait(bar(S_EMPTY + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        tc_fence_after();
+        const uint64_t dK = smem_desc(sK + st * kTileBytes, 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_f16(tS + st * 128, dQ + koff(ks), dK + koff(ks), idesc_qk, ks > 0 ? 1u : 0u);
+        umma_commit(bar(K_EMPTY + st));
+        umma_commit(bar(S_FULL + st));
+      };
+      issue_qk(0);
+      for (int j = 0; j < n; ++j) {
+        if (j + 1 < n) issue_qk(j + 1);  // runs while the softmax warps work on tile j
+        const int st = j & 1;
+        mbar_wait(bar(V_FULL + st), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait(bar(P_FULL), (uint32_t)j & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        tc_fence_after();
+        // MN-major slab of V: 64 d-elements contiguous (128 B), 8-token groups 1024 B apart (stride offset),
+        // the other 64 d-elements 16 KiB further (leading offset); a k-step is 16 tokens = 2048 B.
+        const uint64_t dV = smem_desc(sV + st * kTileBytes, kSlabBytes, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_f16(tO, dP + koff(ks), dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        if (SPLIT) {
+          const uint64_t dPlo = smem_desc(sP + kTileBytes, 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_f16(tO, dPlo + koff(ks), dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, 1u);
+        }
+        umma_commit(bar(V_EMPTY + st));
+        umma_commit(bar(PV_DONE));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one thread per query row
+    const int row = tid;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tO = lane_base + 256;
+    const uint32_t prow = sP + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+    const float sl2 = p.scale_log2;
+    float m_run = -INFINITY, l_run = 0.f;
+    float s[kTile];
+    for (int j = 0; j < n; ++j) {
+      const int b = j & 1;
+      mbar_wait(bar(S_FULL + b), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+      __syncwarp();  // the TMEM loads below are warp-collective
+      tc_fence_after();
+      const uint32_t tS = lane_base + (uint32_t)b * 128u;
+      tmem_ld32<0>(tS, s);
+      tmem_ld32<32>(tS + 32, s);
+      tmem_ld32<64>(tS + 64, s);
+      tmem_ld32<96>(tS + 96, s);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(S_EMPTY + b));  // the buffer may take the logits of tile j + 2
+
+      if (j == qt) {  // diagonal tile: key c of the tile is visible to row r iff c <= r
+#pragma unroll
+        for (int c = 0; c < kTile; ++c)
+          if (c > row) s[c] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, s[c]);
+      mx *= sl2;
+      // Lazy rescaling: the reference point of the exponentials moves only when the row maximum grew by more
+      // than 2^8; until then weights up to 256 are exact enough in 16 bits and O needs no correction.
+      const bool grow = mx > m_run + kRescaleStep;
+      float alpha = 1.f;
+      if (grow) {
+        alpha = exp2f(m_run - mx);
+        m_run = mx;
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < kTile; ++c) {
+        s[c] = exp2f(fmaf(s[c], sl2, -m_run));
+        sum += s[c];
+      }
+      l_run = l_run * alpha + sum;
+
+      if (j > 0) {
+        // P's buffer and O are free once P.V of the previous tile has completed.
+        mbar_wait(bar(PV_DONE), (uint32_t)(j - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        __syncwarp();
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+          float o[32];
+#pragma unroll 1
+          for (int c4 = 0; c4 < 4; ++c4) {
+            tmem_ld32<0>(tO + c4 * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(tO + c4 * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {  // 8 keys = one 16-byte chunk of the row, chunk index XOR (row % 8)
+        const uint32_t addr = prow + (uint32_t)(c8 >> 3) * kSlabBytes + (uint32_t)(((c8 & 7) ^ (row & 7)) << 4);
+        const float* v = s + c8 * 8;
+        if (SPLIT) {
+          uint32_t hi[4], lo[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) split_pair<T>(v[2 * i], v[2 * i + 1], hi[i], lo[i]);
+          sts128(addr, hi[0], hi[1], hi[2], hi[3]);
+          sts128(addr + kTileBytes, lo[0], lo[1], lo[2], lo[3]);
+        } else {
+          sts128(addr, pack_pair<T>(v[0], v[1]), pack_pair<T>(v[2], v[3]), pack_pair<T>(v[4], v[5]),
+                 pack_pair<T>(v[6], v[7]));
+        }
+      }
+      fence_proxy_async_smem();  // generic-proxy writes of P before the MMA's async-proxy reads
+      tc_fence_before();
+      mbar_arrive(bar(P_FULL));
+    }
+
+    mbar_wait(bar(PV_DONE), (uint32_t)(n - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+    __syncwarp();
+    tc_fence_after();
+    const float inv = 1.f / l_run;
+    const bool valid = qt * kTile + row < len;
+    T* orow = static_cast<T*>(p.out) + (int64_t)(start + qt * kTile + row) * p.out_seq_stride +
+              (int64_t)head * p.out_head_stride;
+#pragma unroll 1
+    for (int c4 = 0; c4 < 4; ++c4) {
+      float o[32];
+      tmem_ld32<0>(tO + c4 * 32, o);
+      tmem_wait_ld();
+      if (valid) {
+#pragma unroll
+        for (int v8 = 0; v8 < 4; ++v8) {
+          uint4 w;
+          w.x = pack_pair<T>(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv);
+          w.y = pack_pair<T>(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
+          w.z = pack_pair<T>(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv);
+          w.w = pack_pair<T>(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(orow + c4 * 32 + v8 * 8) = w;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, resolved through the runtime (the library does not link libcuda).
+static int encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (res != cudaDriverEntryPointSuccess || ptr == nullptr) return record_cuda_error(cudaErrorSymbolNotFound);
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  *out = fn;
+  return MUX_OK;
+}
+
+// View [tokens][heads][128] (strides in elements) as a 3-D tensor (d, head, token) fetched in boxes of
+// 64 d-elements x 1 head x 128 tokens with the 128-byte swizzle; rows past the end read as zeros.
+static int make_map(EncodeTiledFn enc, CUtensorMap* map, const void* ptr, int dtype, int64_t tokens, int64_t heads,
+                    int64_t seq_stride, int64_t head_stride) {
+  const cuuint64_t dims[3] = {128, (cuuint64_t)heads, (cuuint64_t)tokens};
+  const cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)seq_stride * 2};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)kTile};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, dtype == MUX_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                         3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MUX_OK : record_cuda_error(cudaErrorInvalidValue);
+}
+
+static bool stride_ok(int64_t seq_stride, int64_t head_stride) {
+  return seq_stride > 0 && head_stride > 0 && seq_stride % 8 == 0 && head_stride % 8 == 0;
+}
+
+template <typename T, bool SPLIT>
+static int launch(const mux_prefill_args_t* a, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                  const Params& prm, cudaStream_t stream) {
+  constexpr int kDevs = 64;
+  static int granted[kDevs] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  if (dev < 0 || dev >= kDevs) return record_cuda_error(cudaErrorInvalidDevice);
+  auto kern = prefill_attn_kernel<T, SPLIT>;
+  constexpr int smem = smem_bytes<SPLIT>();
+  if (granted[dev] < smem) {
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess)
+      return record_cuda_error(e);
+    granted[dev] = smem;
+  }
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((a->max_prompt_len + kTile - 1) / kTile), (unsigned)a->num_q_heads,
+                     (unsigned)a->num_seqs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = pdl;
+  cfg.numAttrs = 1;
+  if ((e = cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, prm)) != cudaSuccess) return record_cuda_error(e);
+  return MUX_OK;
+}
+
+static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
+  if (a == nullptr) return MUX_ERR_NULL_POINTER;
+  if (a->dtype != MUX_DTYPE_F16 && a->dtype != MUX_DTYPE_BF16) return MUX_ERR_BAD_DTYPE;
+  if (a->head_size != 128) return MUX_ERR_BAD_HEAD_SIZE;
+  if (a->num_seqs < 0 || a->total_tokens < 0 || a->max_prompt_len < 0 || a->num_q_heads <= 0 ||
+      a->num_kv_heads <= 0 || !(a->scale > 0.f) || a->num_seqs > 65535 || a->num_q_heads > 65535)
+    return MUX_ERR_BAD_SHAPE;
+  if (a->num_q_heads % a->num_kv_heads != 0) return MUX_ERR_BAD_GROUP;
+  if (a->num_seqs == 0 || a->total_tokens == 0 || a->max_prompt_len == 0) return MUX_OK;
+  if (!a->out || !a->q || !a->k || !a->v || !a->cu_seqlens) return MUX_ERR_NULL_POINTER;
+  if (!aligned16(a->out) || !aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v)) return MUX_ERR_MISALIGNED;
+  if (!stride_ok(a->out_seq_stride, a->out_head_stride) || !stride_ok(a->q_seq_stride, a->q_head_stride) ||
+      !stride_ok(a->k_seq_stride, a->k_head_stride) || !stride_ok(a->v_seq_stride, a->v_head_stride))
+    return MUX_ERR_MISALIGNED;
+  unsigned* status = device_status_ptr();
+  if (status == nullptr) return MUX_ERR_CUDA;
+  EncodeTiledFn enc = nullptr;
+  int st = encode_fn(&enc);
+  if (st != MUX_OK) return st;
+  alignas(64) CUtensorMap mq, mk, mv;
+  if ((st = make_map(enc, &mq, a->q, a->dtype, a->total_tokens, a->num_q_heads, a->q_seq_stride, a->q_head_stride)) ||
+      (st = make_map(enc, &mk, a->k, a->dtype, a->total_tokens, a->num_kv_heads, a->k_seq_stride, a->k_head_stride)) ||
+      (st = make_map(enc, &mv, a->v, a->dtype, a->total_tokens, a->num_kv_heads, a->v_seq_stride, a->v_head_stride)))
+    return st;
+  Params prm;
+  prm.out = a->out;
+  prm.out_seq_stride = a->out_seq_stride;
+  prm.out_head_stride = a->out_head_stride;
+  prm.cu_seqlens = a->cu_seqlens;
+  prm.total_tokens = a->total_tokens;
+  prm.max_prompt_len = a->max_prompt_len;
+  prm.group = a->num_q_heads / a->num_kv_heads;
+  prm.scale_log2 = a->scale * 1.4426950408889634f;
+  prm.status = status;
+  if (a->dtype == MUX_DTYPE_F16) return launch<__half, false>(a, mq, mk, mv, prm, stream);
+  return launch<__nv_bfloat16, true>(a, mq, mk, mv, prm, stream);
+}
+
+}  // namespace prefill
+}  // namespace mux
+
+extern "C" int mux_prefill_attention(const mux_prefill_args_t* args, void* cuda_stream) {
+  return mux::prefill::run(args, static_cast<cudaStream_t>(cuda_stream));
+}

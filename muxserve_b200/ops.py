@@ -347,6 +347,46 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
     launch_count += 0 if n == 0 else (2 if need > 0 else 1)
 
 
+def cu_seqlens_from_prompt_lens(prompt_lens, device) -> torch.Tensor:
+    """int32 [len(prompt_lens) + 1] prefix sums of ``prompt_lens`` (``InputMetadata.prompt_lens``) on ``device``."""
+    cu = [0]
+    for n in prompt_lens:
+        cu.append(cu[-1] + int(n))
+    return torch.tensor(cu, dtype=torch.int32, device=device)
+
+
+def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                      cu_seqlens: torch.Tensor, max_prompt_len: int, scale: float) -> None:
+    """Causal self-attention of every prompt over its own tokens (the prompt branch of PagedAttentionWithRoPE).
+
+    ``q``/``out`` [T, Hq(*128)], ``k``/``v`` [T, H(*128)] hold the rows of all prompts back to back;
+    ``cu_seqlens`` int32 [S + 1] (device) are the row offsets; ``max_prompt_len`` bounds every prompt length."""
+    _require_cuda(out=out, q=q, k=k, v=v, cu_seqlens=cu_seqlens)
+    if cu_seqlens.dtype != torch.int32 or cu_seqlens.dim() != 1 or not cu_seqlens.is_contiguous():
+        raise TypeError("cu_seqlens must be a contiguous int32 [num_seqs + 1] tensor")
+    code = _dtype_code(q, "q")
+    if out.dtype != q.dtype or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("out, q, k and v must have one dtype")
+    T, Hq, q_ss, q_hs = _rows(q, "q")
+    To, Ho, o_ss, o_hs = _rows(out, "out")
+    Tk, Hk, k_ss, k_hs = _rows(k, "k")
+    Tv, Hv, v_ss, v_hs = _rows(v, "v")
+    if (To, Ho) != (T, Hq) or Tk != T or Tv != T or Hv != Hk:
+        raise ValueError("out/q/k/v shapes do not agree")
+    S = cu_seqlens.shape[0] - 1
+    if S < 0:
+        raise ValueError("cu_seqlens needs at least one entry")
+    args = _lib.PrefillArgs(out=out.data_ptr(), q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(),
+                            out_seq_stride=o_ss, out_head_stride=o_hs, q_seq_stride=q_ss, q_head_stride=q_hs,
+                            k_seq_stride=k_ss, k_head_stride=k_hs, v_seq_stride=v_ss, v_head_stride=v_hs,
+                            cu_seqlens=cu_seqlens.data_ptr(), scale=float(scale), num_seqs=S, total_tokens=T,
+                            max_prompt_len=int(max_prompt_len), num_q_heads=Hq, num_kv_heads=Hk,
+                            head_size=HEAD_SIZE, dtype=code, reserved=0)
+    check(lib().mux_prefill_attention(C.byref(args), _stream()), "prefill_attention")
+    global launch_count
+    launch_count += 1 if S > 0 and T > 0 and max_prompt_len > 0 else 0
+
+
 def device_status() -> int:
     """Reads and clears the MUX_DEV_* status bits of the current device (synchronises the stream)."""
     return check(lib().mux_device_status(_stream()), "device_status")

@@ -1,0 +1,90 @@
+"""GPU parity: prompt-phase attention (tcgen05 kernel) against the fp32 oracle, through the C ABI."""
+import pytest
+import torch
+
+from oracle.prefill_oracle import prefill_attention_ref
+from tests.gpu_util import ATOL, RTOL
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(prompt_lens, Hq, H, dtype, seed, strided=False, scale=None):
+    from muxserve_b200 import ops
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(seed)
+    T = int(sum(prompt_lens))
+    scale = scale if scale is not None else 128 ** -0.5
+    if strided:  # q, k, v as the split views of one fused projection output
+        qkv = torch.randn((T, (Hq + 2 * H) * 128), generator=gen).to(dtype).to(dev)
+        q, k, v = qkv.split([Hq * 128, H * 128, H * 128], dim=1)
+    else:
+        q = torch.randn((T, Hq, 128), generator=gen).to(dtype).to(dev)
+        k = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+        v = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    out = torch.full((T, Hq * 128), float("nan"), dtype=dtype, device=dev)
+    cu = ops.cu_seqlens_from_prompt_lens(prompt_lens, dev)
+    ops.prefill_attention(out, q, k, v, cu, max(prompt_lens) if prompt_lens else 0, scale)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    ref = prefill_attention_ref(q.reshape(T, Hq, 128), k.reshape(T, H, 128), v.reshape(T, H, 128), prompt_lens, scale)
+    got = out.float().cpu().view(T, Hq, 128)
+    err = (got - ref).abs()
+    bound = ATOL + RTOL * ref.abs()
+    assert torch.isfinite(got).all()
+    assert (err <= bound).all(), f"max err {err.max().item():.3e} (worst excess {(err - bound).max().item():.3e})"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_single_tile(dtype):
+    _run([128], 2, 2, dtype, 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_ragged_multi_tile(dtype):
+    _run([1, 5, 127, 128, 129, 300, 777], 4, 4, dtype, 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_gqa_and_strided_views(dtype):
+    _run([33, 260, 513], 8, 2, dtype, 3, strided=True)
+
+
+def test_long_prompt_fp16():
+    _run([2048, 1500], 2, 1, torch.float16, 4)
+
+
+def test_large_logits_trigger_rescale():
+    # scale 1.0 on N(0,1) rows gives logits of tens of units: the running maximum keeps growing across tiles
+    _run([640], 2, 2, torch.float16, 5, scale=1.0)
+
+
+def test_empty_and_zero_length():
+    _run([0, 17, 0], 2, 2, torch.float16, 6)
+    from muxserve_b200 import ops
+    dev = torch.device("cuda:0")
+    e = torch.empty((0, 256), dtype=torch.float16, device=dev)
+    ops.prefill_attention(e, e, e, e, torch.zeros(1, dtype=torch.int32, device=dev), 0, 0.1)
+
+
+def test_bad_offsets_are_reported_not_read():
+    from muxserve_b200 import _lib, ops
+    dev = torch.device("cuda:0")
+    q = torch.randn((64, 2, 128), dtype=torch.float16, device=dev)
+    out = torch.zeros_like(q)
+    cu = torch.tensor([0, 9999], dtype=torch.int32, device=dev)   # claims more rows than the tensors hold
+    ops.prefill_attention(out, q, q, q, cu, 64, 0.1)
+    torch.cuda.synchronize()
+    assert ops.device_status() & _lib.MUX_DEV_BAD_CONTEXT
+    assert (out == 0).all()
+
+
+def test_rejects_bad_arguments():
+    from muxserve_b200 import _lib, ops
+    dev = torch.device("cuda:0")
+    q = torch.randn((16, 3, 128), dtype=torch.float16, device=dev)
+    k = torch.randn((16, 2, 128), dtype=torch.float16, device=dev)
+    cu = torch.tensor([0, 16], dtype=torch.int32, device=dev)
+    with pytest.raises(_lib.MuxError):
+        ops.prefill_attention(torch.empty_like(q), q, k, k, cu, 16, 0.1)      # 3 q heads over 2 kv heads
+    with pytest.raises(_lib.MuxError):
+        ops.prefill_attention(torch.empty_like(q), q, q, q, cu, 16, 0.0)      # scale must be positive
