@@ -6,13 +6,13 @@
 // This is the one GEMM-shaped kernel of the library, so it runs on the 5th-generation tensor
 // cores: one CTA owns 128 query rows of one (prompt, q head) and walks the key/value tiles of
 // 128 tokens up to the diagonal.
-//   warp 4 (one lane)  TMA producer: Q once, then K and V tiles through 2-stage rings
+//   warp 8 (one lane)  TMA producer: Q once, then K and V tiles through 2-stage rings
 //                      (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers)
-//   warp 5 (one lane)  issues tcgen05.mma: S = Q.K^T into one of two TMEM buffers, O += P.V
+//   warp 9 (one lane)  issues tcgen05.mma: S = Q.K^T into one of two TMEM buffers, O += P.V
 //                      into a third; tcgen05.commit signals the mbarriers
-//   warps 0-3          one thread per query row: tcgen05.ld of the S row, scale, causal mask,
-//                      online softmax (lazy rescaling of O), P written to shared memory in the
-//                      MMA's K-major swizzled layout, final O / l written to global memory
+//   warps 0-7          two threads per query row (64 columns each): tcgen05.ld of the S row, scale,
+//                      causal mask, online softmax (lazy rescaling of O), P written back to tensor
+//                      memory in place of the logits (the A operand of P.V), final O / l to global memory
 // bf16 rounds P to 8 bits, which breaks the 2e-3 tolerance on short prompts with cancelling
 // values; there P is split into hi + lo parts and P.V takes two MMAs per step.
 // Every wait is bounded (ptx.cuh); TMEM is freed on every path that allocated it.
@@ -31,8 +31,10 @@ namespace prefill {
 constexpr int kTile = 128;                   // query rows per CTA = tokens per K/V tile
 constexpr int kSlabBytes = kTile * 128;      // 128 rows x 64 elements: one 128-byte-swizzled slab
 constexpr int kTileBytes = 2 * kSlabBytes;   // head size 128 = two slabs
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kHalf = kTile / 2;              // columns of a tile one softmax thread handles
+constexpr int kSoftmaxWarps = 8;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 320;
 constexpr uint32_t kTmemCols = 512;          // S0 | S1 | O (3 x 128 fp32 columns), power of two
 constexpr float kRescaleStep = 8.f;          // O is rescaled only when the running max grows by 2^8
 
@@ -62,8 +64,8 @@ struct Params {
 
 template <bool SPLIT>
 constexpr int smem_bytes() {
-  // Q + 2 K + 2 V + P (hi [+ lo]) + barriers, plus slack for the 1024-byte alignment
-  return kTileBytes * (5 + (SPLIT ? 2 : 1)) + 256 + 1024;
+  // Q + 2 K + 2 V + barriers + the softmax halves' exchange buffer
+  return kTileBytes * 5 + 256 + 4 * kTile * 4;
 }
 
 // ---- tcgen05 / TMA building blocks -----------------------------------------------------------
@@ -110,6 +112,18 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// Same with A read from tensor memory: row i of A in lane i, two 16-bit elements per 32-bit column, so a
+// 16-element k-step is 8 columns.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets
 // (all in 16-byte units), descriptor version 1, layout type 2.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -152,6 +166,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&s)[N]) {
       : "memory");
 }
 
+#define MUX_R4I(a, i) "r"(a[i]), "r"(a[i + 1]), "r"(a[i + 2]), "r"(a[i + 3])
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&s)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+      ::MUX_R4I(s, 0), MUX_R4I(s, 4), MUX_R4I(s, 8), MUX_R4I(s, 12), MUX_R4I(s, 16), MUX_R4I(s, 20),
+        MUX_R4I(s, 24), MUX_R4I(s, 28), "r"(taddr)
+      : "memory");
+}
+
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -175,7 +200,7 @@ template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                     const __grid_constant__ CUtensorMap tmv, const Params p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzle pattern repeats every 1024 bytes
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = blockIdx.z, head = blockIdx.y;
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // the tiles with the most work start first
@@ -191,15 +216,19 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
   const int n = qt + 1;  // key/value tiles 0..qt; the last one is the diagonal
 
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
+  if (raw & 1023u) {  // the tiles' swizzle needs the declared alignment; never seen violated, never worked around
+    if (tid == 0) atomicOr(p.status, MUX_DEV_WAIT_TIMEOUT);
+    return;
+  }
+  const uint32_t base = raw;
   const uint32_t sQ = base;
   const uint32_t sK = sQ + kTileBytes;
   const uint32_t sV = sK + 2 * kTileBytes;
-  const uint32_t sP = sV + 2 * kTileBytes;
-  const uint32_t sBar = sP + (SPLIT ? 2 : 1) * kTileBytes;
+  const uint32_t sBar = sV + 2 * kTileBytes;
   auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
   const uint32_t sSlot = sBar + 8u * NUM_BARS;
   volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sSlot - raw));
+  float* xchg = reinterpret_cast<float*>(smem_raw + (sSlot + 16 - raw));  // [2][2][kTile]: row maxima / sums of the halves
 
   if (tid == 0) {
     mbar_init(bar(Q_FULL), 1);
@@ -209,20 +238,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       mbar_init(bar(V_FULL + i), 1);
       mbar_init(bar(V_EMPTY + i), 1);
       mbar_init(bar(S_FULL + i), 1);
-      mbar_init(bar(S_EMPTY + i), kSoftmaxThreads);
+      mbar_init(bar(S_EMPTY + i), kSoftmaxWarps);
     }
-    mbar_init(bar(P_FULL), kSoftmaxThreads);
+    mbar_init(bar(P_FULL), kSoftmaxWarps);
     mbar_init(bar(PV_DONE), 1);
     mbar_init_fence();
   }
-  if (warp == 5) tmem_alloc(sSlot, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(sSlot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *slot;
   griddep_launch_dependents();
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const int kvh = head / p.group;
@@ -249,7 +278,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         mbar_wait(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
@@ -260,7 +289,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       // swizzled row, the second 64-element slab 16 KiB further.
       auto koff = [](int ks) { return (uint64_t)((ks >> 2) * (kSlabBytes >> 4) + (ks & 3) * 2); };
       const uint64_t dQ = smem_desc(sQ, 16, 1024);
-      const uint64_t dP = smem_desc(sP, 16, 1024);
       mbar_wait(bar(Q_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
       auto issue_qk = [&](int j) {
         const int st = j & 1;
@@ -285,51 +313,64 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         // MN-major slab of V: 64 d-elements contiguous (128 B), 8-token groups 1024 B apart (stride offset),
         // the other 64 d-elements 16 KiB further (leading offset); a k-step is 16 tokens = 2048 B.
         const uint64_t dV = smem_desc(sV + st * kTileBytes, kSlabBytes, 1024);
+        // A = P from tensor memory, where the softmax threads left it in place of the logits of this tile
+        const uint32_t tP = tS + st * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_f16(tO, dP + koff(ks), dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_f16_ts(tO, tP + ks * 8, dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         if (SPLIT) {
-          const uint64_t dPlo = smem_desc(sP + kTileBytes, 16, 1024);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_f16(tO, dPlo + koff(ks), dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, 1u);
+            umma_f16_ts(tO, tP + 64 + ks * 8, dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, 1u);
         }
         umma_commit(bar(V_EMPTY + st));
         umma_commit(bar(PV_DONE));
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: one thread per query row
-    const int row = tid;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    const uint32_t tO = lane_base + 256;
-    const uint32_t prow = sP + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+    // ------------------------------------------------------------------ softmax: two threads per query row
+    // Warps w and w + 4 own the same 32 rows (TMEM lanes 32 (w % 4) ...) and split the 128 columns of a tile
+    // in halves, so that every scheduler has two softmax warps to interleave.  The halves share the running
+    // maximum (one exchange through shared memory per tile) and keep partial sums until the end.
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const int col0 = half * kHalf;
+    const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t tO = lane_base + 256 + (uint32_t)col0;
+    float* xmax = xchg + half * kTile + row;             // [parity][half][row]
+    const float* xmax_other = xchg + (half ^ 1) * kTile + row;
     const float sl2 = p.scale_log2;
     float m_run = -INFINITY, l_run = 0.f;
-    float s[kTile];
+    float s[kHalf];
     for (int j = 0; j < n; ++j) {
       const int b = j & 1;
       mbar_wait(bar(S_FULL + b), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
       __syncwarp();  // the TMEM loads below are warp-collective
       tc_fence_after();
-      const uint32_t tS = lane_base + (uint32_t)b * 128u;
+      const uint32_t tS = lane_base + (uint32_t)(b * 128 + col0);
       tmem_ld32<0>(tS, s);
       tmem_ld32<32>(tS + 32, s);
-      tmem_ld32<64>(tS + 64, s);
-      tmem_ld32<96>(tS + 96, s);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(bar(S_EMPTY + b));  // the buffer may take the logits of tile j + 2
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_EMPTY + b));  // one arrival per warp: the logits are in registers
 
       if (j == qt) {  // diagonal tile: key c of the tile is visible to row r iff c <= r
 #pragma unroll
-        for (int c = 0; c < kTile; ++c)
-          if (c > row) s[c] = -INFINITY;
+        for (int c = 0; c < kHalf; ++c)
+          if (col0 + c > row) s[c] = -INFINITY;
       }
-      float mx = s[0];
+      float mx4[4];
 #pragma unroll
-      for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, s[c]);
-      mx *= sl2;
+      for (int i = 0; i < 4; ++i) mx4[i] = s[i];
+#pragma unroll
+      for (int c = 4; c < kHalf; c += 4)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], s[c + i]);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      xmax[b * 2 * kTile] = mx;
+      named_bar_sync(1 + quarter, 64);
+      mx = fmaxf(mx, xmax_other[b * 2 * kTile]) * sl2;
       // Lazy rescaling: the reference point of the exponentials moves only when the row maximum grew by more
       // than 2^8; until then weights up to 256 are exact enough in 16 bits and O needs no correction.
       const bool grow = mx > m_run + kRescaleStep;
@@ -338,63 +379,74 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         alpha = exp2f(m_run - mx);
         m_run = mx;
       }
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < kTile; ++c) {
-        s[c] = exp2f(fmaf(s[c], sl2, -m_run));
-        sum += s[c];
-      }
-      l_run = l_run * alpha + sum;
+      for (int c = 0; c < kHalf; c += 4)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          s[c + i] = exp2f(fmaf(s[c + i], sl2, -m_run));
+          sum4[i] += s[c + i];
+        }
+      l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-      if (j > 0) {
-        // P's buffer and O are free once P.V of the previous tile has completed.
+      // O takes a correction only when some row of the warp moved its reference point (both halves of a row
+      // decide alike); it is free for that once P.V of the previous tile has completed.  The wait is skipped
+      // otherwise: S_FULL of this tile already implies P.V of tile j - 2, so a later wait on PV_DONE is never
+      // more than one phase behind.
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
         mbar_wait(bar(PV_DONE), (uint32_t)(j - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
         __syncwarp();
         tc_fence_after();
-        if (__any_sync(0xffffffffu, grow)) {
-          float o[32];
+        float o[32];
 #pragma unroll 1
-          for (int c4 = 0; c4 < 4; ++c4) {
-            tmem_ld32<0>(tO + c4 * 32, o);
-            tmem_wait_ld();
+        for (int c2 = 0; c2 < 2; ++c2) {
+          tmem_ld32<0>(tO + c2 * 32, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st32(tO + c4 * 32, o);
-          }
-          tmem_wait_st();
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(tO + c2 * 32, o);
         }
       }
-#pragma unroll
-      for (int c8 = 0; c8 < 16; ++c8) {  // 8 keys = one 16-byte chunk of the row, chunk index XOR (row % 8)
-        const uint32_t addr = prow + (uint32_t)(c8 >> 3) * kSlabBytes + (uint32_t)(((c8 & 7) ^ (row & 7)) << 4);
-        const float* v = s + c8 * 8;
+      // P replaces the logits of this tile in tensor memory: two 16-bit weights per column, this thread's 64
+      // keys in 32 columns (the hi parts; the lo parts of the split go 64 columns further).  The other half of
+      // the row has finished reading its logits: it passed the exchange barrier above after its loads.
+      {
+        const uint32_t tP = lane_base + (uint32_t)(b * 128 + half * 32);
+        uint32_t hi[32];
         if (SPLIT) {
-          uint32_t hi[4], lo[4];
+          uint32_t lo[32];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) split_pair<T>(v[2 * i], v[2 * i + 1], hi[i], lo[i]);
-          sts128(addr, hi[0], hi[1], hi[2], hi[3]);
-          sts128(addr + kTileBytes, lo[0], lo[1], lo[2], lo[3]);
+          for (int i = 0; i < 32; ++i) split_pair<T>(s[2 * i], s[2 * i + 1], hi[i], lo[i]);
+          tmem_st32u(tP, hi);
+          tmem_st32u(tP + 64, lo);
         } else {
-          sts128(addr, pack_pair<T>(v[0], v[1]), pack_pair<T>(v[2], v[3]), pack_pair<T>(v[4], v[5]),
-                 pack_pair<T>(v[6], v[7]));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) hi[i] = pack_pair<T>(s[2 * i], s[2 * i + 1]);
+          tmem_st32u(tP, hi);
         }
+        tmem_wait_st();
       }
-      fence_proxy_async_smem();  // generic-proxy writes of P before the MMA's async-proxy reads
       tc_fence_before();
-      mbar_arrive(bar(P_FULL));
+      __syncwarp();  // every lane's stores have completed; lane 0 publishes them for the warp
+      if (lane == 0) mbar_arrive(bar(P_FULL));
     }
 
+    // the two halves of a row add their partial sums (slots of parity n & 1: last written for tile n - 2)
+    xmax[(n & 1) * 2 * kTile] = l_run;
+    named_bar_sync(1 + quarter, 64);
+    l_run += xmax_other[(n & 1) * 2 * kTile];
+    if (n >= 2) mbar_wait(bar(PV_DONE), (uint32_t)(n - 2) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     mbar_wait(bar(PV_DONE), (uint32_t)(n - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     __syncwarp();
     tc_fence_after();
     const float inv = 1.f / l_run;
     const bool valid = qt * kTile + row < len;
     T* orow = static_cast<T*>(p.out) + (int64_t)(start + qt * kTile + row) * p.out_seq_stride +
-              (int64_t)head * p.out_head_stride;
+              (int64_t)head * p.out_head_stride + col0;
 #pragma unroll 1
-    for (int c4 = 0; c4 < 4; ++c4) {
+    for (int c2 = 0; c2 < 2; ++c2) {
       float o[32];
-      tmem_ld32<0>(tO + c4 * 32, o);
+      tmem_ld32<0>(tO + c2 * 32, o);
       tmem_wait_ld();
       if (valid) {
 #pragma unroll
@@ -404,7 +456,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
           w.y = pack_pair<T>(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
           w.z = pack_pair<T>(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv);
           w.w = pack_pair<T>(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
-          *reinterpret_cast<uint4*>(orow + c4 * 32 + v8 * 8) = w;
+          *reinterpret_cast<uint4*>(orow + c2 * 32 + v8 * 8) = w;
         }
       }
     }
@@ -412,7 +464,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
