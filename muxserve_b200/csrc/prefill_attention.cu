@@ -6,10 +6,10 @@
 // This is the one GEMM-shaped kernel of the library, so it runs on the 5th-generation tensor
 // cores: one CTA owns 128 query rows of one (prompt, q head) and walks the key/value tiles of
 // 128 tokens up to the diagonal.
-//   warp 8 (one lane)  TMA producer: Q once, then K and V tiles through 2-stage rings
+//   warp 8 (one lane)  TMA producer: Q once, then K and V tiles through a 3-stage ring
 //                      (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers)
-//   warp 9 (one lane)  issues tcgen05.mma: S = Q.K^T into one of two TMEM buffers, O += P.V
-//                      into a third; tcgen05.commit signals the mbarriers
+//   warp 9 (one lane)  issues tcgen05.mma with A in tensor memory: S = Q.K^T into one of two TMEM
+//                      buffers, O += P.V into a third; tcgen05.commit signals the mbarriers
 //   warps 0-7          two threads per query row (64 columns each): tcgen05.ld of the S row, scale,
 //                      causal mask, online softmax (lazy rescaling of O), P written back to tensor
 //                      memory in place of the logits (the A operand of P.V), final O / l to global memory
@@ -35,20 +35,19 @@ constexpr int kHalf = kTile / 2;              // columns of a tile one softmax t
 constexpr int kSoftmaxWarps = 8;
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr int kThreads = 320;
-constexpr uint32_t kTmemCols = 512;          // S0 | S1 | O (3 x 128 fp32 columns), power of two
+constexpr uint32_t kTmemCols = 512;          // S0 | S1 | O | Q (448 columns used), power of two
 constexpr float kRescaleStep = 8.f;          // O is rescaled only when the running max grows by 2^8
 
+constexpr int kStages = 3;                    // K/V ring: two tiles in flight while one is consumed
+
 enum Bar {
-  Q_FULL = 0,
-  K_FULL = 1,   // +stage
-  K_EMPTY = 3,
-  V_FULL = 5,
-  V_EMPTY = 7,
-  S_FULL = 9,   // +buffer
-  S_EMPTY = 11,
-  P_FULL = 13,
-  PV_DONE = 14,
-  NUM_BARS = 15
+  Q_FULL = 0,                  // TMA bytes of Q have landed
+  QT_FULL = 1,                 // the softmax warps have moved Q to tensor memory
+  P_FULL = 2,
+  KV_FULL = 3,                 // + ring stage
+  S_FULL = KV_FULL + kStages,
+  PV_DONE = S_FULL + kStages,
+  NUM_BARS = PV_DONE + kStages
 };
 
 struct Params {
@@ -64,8 +63,8 @@ struct Params {
 
 template <bool SPLIT>
 constexpr int smem_bytes() {
-  // Q + 2 K + 2 V + barriers + the softmax halves' exchange buffer
-  return kTileBytes * 5 + 256 + 4 * kTile * 4;
+  // Q + K/V ring + barriers + the softmax halves' exchange buffer
+  return kTileBytes * (1 + 2 * kStages) + 256 + 4 * kTile * 4;
 }
 
 // ---- tcgen05 / TMA building blocks -----------------------------------------------------------
@@ -101,19 +100,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem], 128 x 128 x 16, 16-bit operands, fp32 accumulate.
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// Same with A read from tensor memory: row i of A in lane i, two 16-bit elements per 32-bit column, so a
-// 16-element k-step is 8 columns.
+// D[tmem] (+)= A[tmem] * B[smem], 128 x 128 x 16, 16-bit operands, fp32 accumulate.  Row i of A lies in
+// lane i, two 16-bit elements per 32-bit column, so a 16-element k-step is 8 columns.
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
   asm volatile(
@@ -177,8 +165,8 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&s)[3
       : "memory");
 }
 
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
 }
 
 template <typename T>
@@ -195,6 +183,20 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
+//
+// Tensor memory (512 columns x 128 lanes, lane = query row):
+//   [0,128) and [128,256)  logits S of tile j in buffer j & 1; the softmax threads overwrite them with the
+//                          16-bit weights P (64 columns hi [+ 64 columns lo]), the A operand of P.V
+//   [256,384)              O accumulator
+//   [384,448)              Q, 16-bit pairs: the A operand of Q.K^T (read from shared memory once)
+// Barriers (index = ring stage j % kStages unless noted):
+//   KV_FULL   TMA bytes of K and V of tile j have landed
+//   S_FULL    Q.K^T of tile j has completed: logits readable
+//   P_FULL    (single) all 8 softmax warps have written P of tile j (they loaded S of tile j before)
+//   PV_DONE   P.V of tile j has completed: the stage's shared memory is free, O holds tiles 0..j
+// The issuing thread never needs an "S buffer free" signal: it issues Q.K^T of tile j + 1 after it has
+// seen P_FULL of tile j - 1 and after it has issued P.V of tile j - 1, and tcgen05.mma of one thread
+// execute in issue order.
 
 template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -220,11 +222,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     if (tid == 0) atomicOr(p.status, MUX_DEV_WAIT_TIMEOUT);
     return;
   }
-  const uint32_t base = raw;
-  const uint32_t sQ = base;
-  const uint32_t sK = sQ + kTileBytes;
-  const uint32_t sV = sK + 2 * kTileBytes;
-  const uint32_t sBar = sV + 2 * kTileBytes;
+  const uint32_t sQ = raw;
+  const uint32_t sKV = sQ + kTileBytes;  // stage: K tile, then V tile
+  const uint32_t sBar = sKV + kStages * 2 * kTileBytes;
   auto bar = [&](int i) { return sBar + 8u * (uint32_t)i; };
   const uint32_t sSlot = sBar + 8u * NUM_BARS;
   volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sSlot - raw));
@@ -232,16 +232,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
 
   if (tid == 0) {
     mbar_init(bar(Q_FULL), 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(K_FULL + i), 1);
-      mbar_init(bar(K_EMPTY + i), 1);
-      mbar_init(bar(V_FULL + i), 1);
-      mbar_init(bar(V_EMPTY + i), 1);
+    mbar_init(bar(QT_FULL), kSoftmaxWarps);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(bar(KV_FULL + i), 1);
       mbar_init(bar(S_FULL + i), 1);
-      mbar_init(bar(S_EMPTY + i), kSoftmaxWarps);
+      mbar_init(bar(PV_DONE + i), 1);
     }
     mbar_init(bar(P_FULL), kSoftmaxWarps);
-    mbar_init(bar(PV_DONE), 1);
     mbar_init_fence();
   }
   if (warp == kMmaWarp) tmem_alloc(sSlot, kTmemCols);
@@ -260,61 +257,52 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       tma_load_3d(sQ, &tmq, 0, head, q0, bar(Q_FULL));
       tma_load_3d(sQ + kSlabBytes, &tmq, 64, head, q0, bar(Q_FULL));
       for (int j = 0; j < n; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        const int st = j % kStages;
+        const uint32_t ph = (uint32_t)(j / kStages) & 1u;
         const int t0 = start + j * kTile;
-        mbar_wait(bar(K_EMPTY + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
-        mbar_arrive_expect_tx(bar(K_FULL + st), kTileBytes);
-        tma_load_3d(sK + st * kTileBytes, &tmk, 0, kvh, t0, bar(K_FULL + st));
-        tma_load_3d(sK + st * kTileBytes + kSlabBytes, &tmk, 64, kvh, t0, bar(K_FULL + st));
-        mbar_wait(bar(V_EMPTY + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
-        mbar_arrive_expect_tx(bar(V_FULL + st), kTileBytes);
-        tma_load_3d(sV + st * kTileBytes, &tmv, 0, kvh, t0, bar(V_FULL + st));
-        tma_load_3d(sV + st * kTileBytes + kSlabBytes, &tmv, 64, kvh, t0, bar(V_FULL + st));
+        const uint32_t dst = sKV + st * 2 * kTileBytes;
+        mbar_wait(bar(PV_DONE + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);  // P.V of tile j - kStages
+        mbar_arrive_expect_tx(bar(KV_FULL + st), 2 * kTileBytes);
+        tma_load_3d(dst, &tmk, 0, kvh, t0, bar(KV_FULL + st));
+        tma_load_3d(dst + kSlabBytes, &tmk, 64, kvh, t0, bar(KV_FULL + st));
+        tma_load_3d(dst + kTileBytes, &tmv, 0, kvh, t0, bar(KV_FULL + st));
+        tma_load_3d(dst + kTileBytes + kSlabBytes, &tmv, 64, kvh, t0, bar(KV_FULL + st));
       }
       // No copy of this CTA may still be in flight when it ends (matters only after a failed wait).
-      for (int j = (n > 2 ? n - 2 : 0); j < n; ++j) {
-        mbar_wait(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
-        mbar_wait(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
-      }
+      for (int j = (n > kStages ? n - kStages : 0); j < n; ++j)
+        mbar_wait(bar(KV_FULL + j % kStages), (uint32_t)(j / kStages) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-      constexpr uint32_t idesc_qk = instr_desc(fmt, 0);  // S = Q K^T: both operands K-major (d contiguous)
+      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t idesc_qk = instr_desc(fmt, 0);  // S = Q K^T: K tile K-major (d contiguous)
       constexpr uint32_t idesc_pv = instr_desc(fmt, 1);  // O = P V: V is MN-major (d contiguous, tokens = K)
-      const uint32_t tS = tmem, tO = tmem + 256;
-      // K-major slab: rows 128 B apart, 8-row groups 1024 B apart; a 16-element k-step is 32 B inside the
-      // swizzled row, the second 64-element slab 16 KiB further.
-      auto koff = [](int ks) { return (uint64_t)((ks >> 2) * (kSlabBytes >> 4) + (ks & 3) * 2); };
-      const uint64_t dQ = smem_desc(sQ, 16, 1024);
-      mbar_wait(bar(Q_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
+      const uint32_t tS = tmem, tO = tmem + 256, tQ = tmem + 384;
+      mbar_wait(bar(QT_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
       auto issue_qk = [&](int j) {
-        const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        mbar_wait(bar(K_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
-        mbar_wait(bar(S_EMPTY + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        const int st = j % kStages;
+        mbar_wait(bar(KV_FULL + st), (uint32_t)(j / kStages) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
         tc_fence_after();
-        const uint64_t dK = smem_desc(sK + st * kTileBytes, 16, 1024);
+        // K-major slab: rows 128 B apart, 8-row groups 1024 B apart; a 16-element k-step is 32 B inside the
+        // swizzled row, the second 64-element slab 16 KiB further.  A: 8 columns of Q per k-step.
+        const uint64_t dK = smem_desc(sKV + st * 2 * kTileBytes, 16, 1024);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_f16(tS + st * 128, dQ + koff(ks), dK + koff(ks), idesc_qk, ks > 0 ? 1u : 0u);
-        umma_commit(bar(K_EMPTY + st));
+          umma_f16_ts(tS + (j & 1) * 128, tQ + ks * 8, dK + (uint64_t)((ks >> 2) * (kSlabBytes >> 4) + (ks & 3) * 2),
+                      idesc_qk, ks > 0 ? 1u : 0u);
         umma_commit(bar(S_FULL + st));
       };
       issue_qk(0);
       for (int j = 0; j < n; ++j) {
         if (j + 1 < n) issue_qk(j + 1);  // runs while the softmax warps work on tile j
-        const int st = j & 1;
-        mbar_wait(bar(V_FULL + st), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        const int st = j % kStages;
         mbar_wait(bar(P_FULL), (uint32_t)j & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
         tc_fence_after();
         // MN-major slab of V: 64 d-elements contiguous (128 B), 8-token groups 1024 B apart (stride offset),
         // the other 64 d-elements 16 KiB further (leading offset); a k-step is 16 tokens = 2048 B.
-        const uint64_t dV = smem_desc(sV + st * kTileBytes, kSlabBytes, 1024);
-        // A = P from tensor memory, where the softmax threads left it in place of the logits of this tile
-        const uint32_t tP = tS + st * 128;
+        const uint64_t dV = smem_desc(sKV + st * 2 * kTileBytes + kTileBytes, kSlabBytes, 1024);
+        const uint32_t tP = tS + (j & 1) * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           umma_f16_ts(tO, tP + ks * 8, dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
@@ -323,8 +311,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
           for (int ks = 0; ks < 8; ++ks)
             umma_f16_ts(tO, tP + 64 + ks * 8, dV + (uint64_t)(ks * (2048 >> 4)), idesc_pv, 1u);
         }
-        umma_commit(bar(V_EMPTY + st));
-        umma_commit(bar(PV_DONE));
+        umma_commit(bar(PV_DONE + st));
       }
     }
   } else {
@@ -340,20 +327,36 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     float* xmax = xchg + half * kTile + row;             // [parity][half][row]
     const float* xmax_other = xchg + (half ^ 1) * kTile + row;
     const float sl2 = p.scale_log2;
+
+    // Q moves to tensor memory once: Q.K^T then fetches only K from shared memory (with both operands in
+    // shared memory a 128 x 128 x 16 MMA needs all of its bandwidth).  This thread's 64 elements are one row
+    // of one slab; chunk c of the row lies at chunk c ^ (row % 8).
+    mbar_wait(bar(Q_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
+    {
+      uint32_t qv[32];
+      const uint32_t qrow = sQ + (uint32_t)half * kSlabBytes + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8)
+        lds128(qrow + (uint32_t)((c8 ^ (row & 7)) << 4), qv[c8 * 4], qv[c8 * 4 + 1], qv[c8 * 4 + 2], qv[c8 * 4 + 3]);
+      __syncwarp();
+      tmem_st32u(lane_base + 384 + (uint32_t)(half * 32), qv);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(QT_FULL));
+    }
+
     float m_run = -INFINITY, l_run = 0.f;
     float s[kHalf];
     for (int j = 0; j < n; ++j) {
       const int b = j & 1;
-      mbar_wait(bar(S_FULL + b), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+      mbar_wait(bar(S_FULL + j % kStages), (uint32_t)(j / kStages) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
       __syncwarp();  // the TMEM loads below are warp-collective
       tc_fence_after();
       const uint32_t tS = lane_base + (uint32_t)(b * 128 + col0);
       tmem_ld32<0>(tS, s);
       tmem_ld32<32>(tS + 32, s);
       tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(S_EMPTY + b));  // one arrival per warp: the logits are in registers
 
       if (j == qt) {  // diagonal tile: key c of the tile is visible to row r iff c <= r
 #pragma unroll
@@ -391,10 +394,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
 
       // O takes a correction only when some row of the warp moved its reference point (both halves of a row
       // decide alike); it is free for that once P.V of the previous tile has completed.  The wait is skipped
-      // otherwise: S_FULL of this tile already implies P.V of tile j - 2, so a later wait on PV_DONE is never
-      // more than one phase behind.
+      // otherwise.
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        mbar_wait(bar(PV_DONE), (uint32_t)(j - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait(bar(PV_DONE + (j - 1) % kStages), (uint32_t)((j - 1) / kStages) & 1u, p.status,
+                  MUX_DEV_WAIT_TIMEOUT);
         __syncwarp();
         tc_fence_after();
         float o[32];
@@ -435,8 +438,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     xmax[(n & 1) * 2 * kTile] = l_run;
     named_bar_sync(1 + quarter, 64);
     l_run += xmax_other[(n & 1) * 2 * kTile];
-    if (n >= 2) mbar_wait(bar(PV_DONE), (uint32_t)(n - 2) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
-    mbar_wait(bar(PV_DONE), (uint32_t)(n - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+    mbar_wait(bar(PV_DONE + (n - 1) % kStages), (uint32_t)((n - 1) / kStages) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     __syncwarp();
     tc_fence_after();
     const float inv = 1.f / l_run;
