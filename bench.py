@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the decode attention path (reshape_and_cache + paged_attention over all layers).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c5] [--impl native|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|prefill] [--impl native|reference]
 
 A step is one decode step of the path: for every layer one cache write of the new
 tokens and one paged attention over the sequence batch.  Prints ONE JSON line.
@@ -59,7 +59,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["c3"], default="c2")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["c3", "prefill"], default="c2")
     ap.add_argument("--pool-frac", type=float, default=0.6, help="fraction of HBM given to the KV pool")
     ap.add_argument("--partition-size", type=int, default=0)
     ap.add_argument("--num-stages", type=int, default=0)
@@ -724,14 +724,202 @@ def run_native_c3(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- prompt phase (secondary workload)
+PREFILL = dict(desc="LLaMA-7B shape fp16 prompt phase: 32 layers, 32 heads (MHA), head_dim 128, 16 prompts with lengths "
+                    "U[128,2048] (the context range of config 2), block_size 16; per layer causal prompt attention + "
+                    "cache write of every prompt token",
+               L=32, Hq=32, H=32, S=16, lo=128, hi=2048, dtype="f16")
+PREFILL_METRIC = ("prompt-phase tokens/s (prompt attention + prompt cache write over all layers; achieved tensor TFLOP/s "
+                  "of the attention kernel and fraction of peak in `roofline`)")
+
+
+def tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops_sustained"]), \
+                "measured (MEASURED_PEAKS.json bf16_tflops_sustained: the kernel is timed inside a long step)"
+        except Exception:
+            pass
+    return 1400.0, "fallback 1400 TFLOP/s sustained (MEASURED_PEAKS.json absent)"
+
+
+def run_native_prefill(args):
+    import torch.distributed as dist
+    from muxserve_b200 import flexstore, ops, workloads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl native needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = dict(PREFILL)
+    if args.layers > 0:
+        w["L"] = args.layers
+    if args.batch > 0:
+        w["S"] = args.batch
+    dt = DTYPES[w["dtype"]]
+    L, Hq, H, S = w["L"], w["Hq"], w["H"], w["S"]
+    gen = torch.Generator().manual_seed(args.seed)           # every replica draws the same prompts
+    lens = workloads.uniform_context_lens(S, w["lo"], w["hi"], gen)
+    T = int(lens.sum())
+    max_len = int(lens.max())
+    nblk = workloads.blocks_needed(lens, L, H, BLOCK)
+    num_blocks = nblk + 1024
+    kc, vc = flexstore.allocate_gpu_cache(num_blocks, BLOCK, dt, dev)
+    perm = torch.randperm(num_blocks, generator=gen).to(dev)
+    tables, _ = workloads.scatter_block_tables(lens, L, H, BLOCK, perm)
+    slots = workloads.prompt_slots(tables, lens, BLOCK)      # [T, L, H]
+    Lq = min(L, 4)                                           # distinct per-layer inputs, cycled
+    q = torch.randn((Lq, T, Hq, 128), generator=gen).to(dt).to(dev)
+    k = torch.randn((Lq, T, H, 128), generator=gen).to(dt).to(dev)
+    v = torch.randn((Lq, T, H, 128), generator=gen).to(dt).to(dev)
+    out = torch.empty((T, Hq, 128), dtype=dt, device=dev)
+    cu = ops.cu_seqlens_from_prompt_lens(lens.tolist(), dev)
+    scale = 128 ** -0.5
+    slot_layers = [slots[:, l, :] for l in range(L)]
+
+    def step():
+        for l in range(L):
+            i = l % Lq
+            ops.prefill_attention(out, q[i], k[i], v[i], cu, max_len, scale)
+            ops.reshape_and_cache(k[i], v[i], kc, vc, slot_layers[l])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    launches0 = ops.launch_count
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = ops.launch_count - launches0
+    # attention kernel alone: events around every attention launch of a few more steps
+    att_ms = []
+    for _ in range(3):
+        evs = []
+        for l in range(L):
+            i = l % Lq
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            ops.prefill_attention(out, q[i], k[i], v[i], cu, max_len, scale)
+            b.record(stream)
+            ops.reshape_and_cache(k[i], v[i], kc, vc, slot_layers[l])
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        att_ms += [a.elapsed_time(b) for a, b in evs]
+    att = sum(att_ms) / len(att_ms)
+    status = ops.device_status()
+    # e2e: what the host supplies per step in the reference (prompt lengths -> cu_seqlens, the [T, L, H] int64
+    # slot mapping) goes up from pinned memory, the last-token rows the sampler reads come back
+    cu_h = cu.cpu().pin_memory()
+    slots_h = slots.cpu().pin_memory()
+    last_rows = (cu[1:].long() - 1)
+    last_h = torch.empty((S, Hq, 128), dtype=dt).pin_memory()
+    cu_d, slots_d = torch.empty_like(cu), torch.empty_like(slots)
+
+    def e2e_step():
+        cu_d.copy_(cu_h, non_blocking=True)
+        slots_d.copy_(slots_h, non_blocking=True)
+        for l in range(L):
+            i = l % Lq
+            ops.prefill_attention(out, q[i], k[i], v[i], cu_d, max_len, scale)
+            ops.reshape_and_cache(k[i], v[i], kc, vc, slots_d[:, l, :])
+        last_h.copy_(out[last_rows], non_blocking=True)
+
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, att], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, att = (float(x) for x in t)
+    if rank == 0:
+        flops = workloads.prefill_flops(lens.tolist(), Hq)
+        peak, peak_src = tensor_peak()
+        achieved = flops / (att * 1e-3) / 1e12
+        line = {
+            "metric": PREFILL_METRIC, "value": T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": f"prefill: {w['desc']}", "prompt_tokens": T, "max_prompt_len": max_len,
+                       "block_size": BLOCK, "seed": args.seed, "replicas": world,
+                       "l2": "no flush: one step streams q/k/v of 4 distinct layers and writes a fresh region of the pool"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "prefill_attn_kernel", "kernel_ms": att,
+                         "flops": "useful causal FLOPs: 4*128 per (query, visible key) and q head"},
+            "gpu_launches": launches, "clocks": clocks, "device_status": status,
+        }
+        if not args.no_e2e:
+            line["e2e"] = {"value": T * world / (e2e_ms * 1e-3), "unit": "tokens/s",
+                           "h2d_bytes_per_step": cu_h.numel() * 4 + slots_h.numel() * 8,
+                           "d2h_bytes_per_step": last_h.numel() * last_h.element_size()}
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = prefill_cpu_baseline(w, lens, args)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def prefill_cpu_baseline(w, lens, args):
+    """Oracle port on the host cores: one layer of the shortest prompts that fill the time budget."""
+    from oracle.prefill_oracle import prefill_attention_ref
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(args.seed + 1)
+    sample = sorted(lens.tolist())[:max(1, len(lens) // 4)]
+    T = sum(sample)
+    dt = DTYPES[w["dtype"]]
+    q = torch.randn((T, w["Hq"], 128), generator=gen).to(dt)
+    k = torch.randn((T, w["H"], 128), generator=gen).to(dt)
+    v = torch.randn((T, w["H"], 128), generator=gen).to(dt)
+    times = []
+    t_all = time.perf_counter()
+    while not times or (time.perf_counter() - t_all < args.cpu_seconds and len(times) < 50):
+        t0 = time.perf_counter()
+        prefill_attention_ref(q, k, v, sample, 128 ** -0.5)
+        times.append(time.perf_counter() - t0)
+    per_layer = sum(times) / len(times)
+    return {"value": T / (per_layer * w["L"]), "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"attention of one of {w['L']} layers over the {len(sample)} shortest prompts ({T} tokens), "
+                      f"{len(times)} repetitions; tokens/s = tokens / (layer time x {w['L']})"}
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
-        if args.workload == "c3":
+        if args.workload in ("c3", "prefill"):
             raise SystemExit("--impl reference supports c2, c4, c5")
         run_reference(args)
     elif args.workload == "c3":
         run_native_c3(args)
+    elif args.workload == "prefill":
+        run_native_prefill(args)
     else:
         run_native(args)
 

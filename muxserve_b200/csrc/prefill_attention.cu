@@ -123,9 +123,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-// Instruction descriptor: fp32 accumulator, a/b format (0 f16, 1 bf16), B major (0 K, 1 MN), N = 128, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t b_mn_major) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: fp32 accumulator, formats of A and of B (0 f16, 1 bf16), B major (0 K, 1 MN),
+// N = 128, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t a_fmt, uint32_t b_fmt, uint32_t b_mn_major) {
+  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 #define MUX_F4(a, i) "=f"(a[i]), "=f"(a[i + 1]), "=f"(a[i + 2]), "=f"(a[i + 3])
@@ -276,8 +277,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-      constexpr uint32_t idesc_qk = instr_desc(fmt, 0);  // S = Q K^T: K tile K-major (d contiguous)
-      constexpr uint32_t idesc_pv = instr_desc(fmt, 1);  // O = P V: V is MN-major (d contiguous, tokens = K)
+      constexpr uint32_t idesc_qk = instr_desc(fmt, fmt, 0);  // S = Q K^T: K tile K-major (d contiguous)
+      // O = P V: V is MN-major (d contiguous, tokens = K).  A and B must have ONE format: fp16 weights over
+      // bf16 values (a_fmt 0, b_fmt 1) raise "illegal instruction" on B200, hence the hi/lo split for bf16.
+      constexpr uint32_t idesc_pv = instr_desc(fmt, fmt, 1);
       const uint32_t tS = tmem, tO = tmem + 256, tQ = tmem + 384;
       mbar_wait(bar(QT_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
       auto issue_qk = [&](int j) {

@@ -113,6 +113,29 @@ def last_token_slots(block_tables: torch.Tensor, context_lens: torch.Tensor, blo
     return out.view(S * new_tokens, L, H)
 
 
+def prompt_slots(block_tables: torch.Tensor, prompt_lens: torch.Tensor, block_size: int) -> torch.Tensor:
+    """Slots of EVERY token of every prompt: int64 [sum(prompt_lens), L, H], prompts back to back — what the
+    reference hands to the prompt-phase cache write (getPromptSlots, csrc/batch_scheduler.h:42-56)."""
+    L, S, H, _ = block_tables.shape
+    dev = block_tables.device
+    lens = prompt_lens.to(torch.int64).cpu()
+    out = torch.empty((int(lens.sum()), L, H), dtype=torch.int64, device=dev)
+    row = 0
+    for s in range(S):
+        n = int(lens[s])
+        pos = torch.arange(n, device=dev)
+        ids = block_tables[:, s, :, :(n + block_size - 1) // block_size].to(torch.int64)   # [L, H, nblk]
+        blk = ids[:, :, pos // block_size]                                                   # [L, H, n]
+        out[row:row + n] = (blk * block_size + (pos % block_size)).permute(2, 0, 1)
+        row += n
+    return out
+
+
+def prefill_flops(prompt_lens: Sequence[int], num_q_heads: int) -> int:
+    """Useful FLOPs of one causal prompt attention launch: 4 * 128 per (query, visible key) pair and q head."""
+    return 4 * HEAD_SIZE * num_q_heads * int(sum(int(n) * (int(n) + 1) // 2 for n in prompt_lens))
+
+
 def make_decode_case(shape: ModelShape, context_lens: torch.Tensor, *, block_size: int, num_blocks: int,
                      dtype: torch.dtype, device, seed: int, block_ids: Optional[torch.Tensor] = None,
                      first_block: int = 0, input_layers: Optional[int] = None, new_tokens: int = 1,

@@ -85,3 +85,66 @@ def test_cache_write_empty_and_errors(env):
         ops.reshape_and_cache(k.bfloat16(), k.bfloat16(), kc, vc, torch.zeros(1, 2, dtype=torch.int64, device="cuda"))
     with pytest.raises(RuntimeError):
         ops.reshape_and_cache(k.cpu(), k.cpu(), kc, vc, torch.zeros(1, 2, dtype=torch.int64))
+
+
+# ---- many tokens: the run-based kernel (taken from 256 tokens up) ----------------------------------------
+def _check_against_oracle(ops, k, v, kc, vc, slots):
+    from oracle.cache_write_oracle import reshape_and_cache_ref
+    kc_c, vc_c = kc.cpu().clone(), vc.cpu().clone()
+    ops.reshape_and_cache(k, v, kc, vc, slots)
+    T, H = slots.shape
+    reshape_and_cache_ref(k.cpu().reshape(T, H, 128), v.cpu().reshape(T, H, 128), kc_c, vc_c, slots.cpu())
+    assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
+    assert torch.equal(vc.cpu().view(torch.int16), vc_c.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B", [8, 16, 32])
+def test_prompt_cache_write_bit_exact(env, dtype, B):
+    """Every token of ragged prompts, slots as the reference's getPromptSlots gives them (csrc/batch_scheduler.h:42-56)."""
+    ops, gu = env
+    from muxserve_b200 import flexstore, workloads
+    gen = torch.Generator().manual_seed(100 + B)
+    lens = torch.tensor([300, 17, 1000, 5, 64, 1, 2 * B], dtype=torch.int32)
+    L, H, nblk = 2, 3, 2048
+    tables, _ = workloads.scatter_block_tables(lens, L, H, B, torch.randperm(nblk, generator=gen).cuda())
+    slots = workloads.prompt_slots(tables, lens, B)          # [T, L, H]
+    T = int(lens.sum())
+    qkv = torch.randn((T, 5 * H * 128), generator=gen).to(dtype).cuda()       # k, v as strided views
+    k, v = qkv[:, H * 128:2 * H * 128], qkv[:, 3 * H * 128:4 * H * 128]
+    kc, vc = flexstore.allocate_gpu_cache(nblk, B, dtype, "cuda")
+    workloads.fill_pool_(kc, vc, 7)
+    _check_against_oracle(ops, k, v, kc, vc, slots[:, 1, :])
+    assert ops.device_status() == 0
+
+
+def test_many_token_cache_write_unaligned_runs(env):
+    """Eight new tokens per sequence starting at arbitrary offsets: short runs that straddle blocks and CTAs' windows."""
+    ops, gu = env
+    ctx = [8 + 3 * i for i in range(44)]                   # 352 rows
+    case, kc, vc = gu.make_case(len(ctx), 4, 2, ctx, 16, torch.float16, seed=78, num_blocks=1024, new_tokens=8)
+    _check_against_oracle(ops, case.k[0], case.v[0], kc, vc, case.slot_mapping[:, 0, :])
+    assert ops.device_status() == 0
+
+
+def test_many_token_cache_write_scattered_padding_and_bad_slots(env):
+    ops, gu = env
+    from muxserve_b200 import _lib
+    gen = torch.Generator().manual_seed(9)
+    T, H, B, nblk = 300, 2, 16, 128
+    slots = torch.randperm(nblk * B, generator=gen)[:T * H].view(T, H).clone()
+    slots[5, 0] = -1                   # padding rows are skipped silently
+    slots[64, 1] = -1
+    slots[100, 0] = nblk * B + 3       # outside the pool: skipped and reported
+    k = torch.randn((T, H, 128), generator=gen).half().cuda()
+    v = torch.randn((T, H, 128), generator=gen).half().cuda()
+    kc = torch.zeros(nblk, 16, B, 8, dtype=torch.float16, device="cuda")
+    vc = torch.zeros(nblk, 128, B, dtype=torch.float16, device="cuda")
+    ok = slots.clone()
+    ok[100, 0] = -1
+    from oracle.cache_write_oracle import reshape_and_cache_ref
+    kc_c, vc_c = kc.cpu().clone(), vc.cpu().clone()
+    ops.reshape_and_cache(k, v, kc, vc, slots.cuda())
+    reshape_and_cache_ref(k.cpu(), v.cpu(), kc_c, vc_c, ok)
+    assert torch.equal(kc.cpu(), kc_c) and torch.equal(vc.cpu(), vc_c)
+    assert ops.device_status() == _lib.MUX_DEV_BAD_SLOT
