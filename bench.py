@@ -65,6 +65,8 @@ def parse_args():
     ap.add_argument("--num-stages", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (small profiler captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the batch size (small profiler captures)")
+    ap.add_argument("--prompt-len", type=int, default=0, help="prefill workload: every prompt has this length")
+    ap.add_argument("--heads", type=int, default=0, help="prefill workload: override the head count (small captures)")
     ap.add_argument("--seed", type=int, default=20240531)
     ap.add_argument("--eager", action="store_true",
                     help="time Python-issued launches instead of replaying a CUDA graph of one step")
@@ -762,6 +764,10 @@ def run_native_prefill(args):
         w["L"] = args.layers
     if args.batch > 0:
         w["S"] = args.batch
+    if args.heads > 0:
+        w["Hq"] = w["H"] = args.heads
+    if args.prompt_len > 0:
+        w["lo"] = w["hi"] = args.prompt_len
     dt = DTYPES[w["dtype"]]
     L, Hq, H, S = w["L"], w["Hq"], w["H"], w["S"]
     gen = torch.Generator().manual_seed(args.seed)           # every replica draws the same prompts
@@ -866,7 +872,8 @@ def run_native_prefill(args):
             "metric": PREFILL_METRIC, "value": T * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": f"prefill: {w['desc']}", "prompt_tokens": T, "max_prompt_len": max_len,
+            "config": {"workload": f"prefill: {w['desc']}", "layers": L, "heads": Hq, "prompts": S,
+                       "prompt_len_range": [w["lo"], w["hi"]], "prompt_tokens": T, "max_prompt_len": max_len,
                        "block_size": BLOCK, "seed": args.seed, "replicas": world,
                        "l2": "no flush: one step streams q/k/v of 4 distinct layers and writes a fresh region of the pool"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",

@@ -48,6 +48,7 @@ typedef enum { MUX_DTYPE_F16 = 0, MUX_DTYPE_BF16 = 1 } mux_dtype_t;
 #define MUX_DEV_BAD_CONTEXT 4u    /* a context length above max_context_len (or < 0) was met */
 #define MUX_DEV_BAD_SLOT 8u       /* a slot outside the pool was met and skipped */
 #define MUX_DEV_BAD_HEAD_MAPPING 16u /* head_mapping does not give every kv head num_q_heads/num_kv_heads q heads */
+#define MUX_DEV_INTERNAL 32u      /* a kernel found a precondition of its own broken (shared-memory alignment) and left */
 
 const char* mux_strerror(int status);
 /* cudaError_t of the last failing CUDA call made by this library on the calling thread. */

@@ -19,6 +19,7 @@ MUX_DEV_WAIT_TIMEOUT = 2
 MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
+MUX_DEV_INTERNAL = 32
 
 ABI_VERSION = 6
 

@@ -88,3 +88,11 @@ def test_rejects_bad_arguments():
         ops.prefill_attention(torch.empty_like(q), q, k, k, cu, 16, 0.1)      # 3 q heads over 2 kv heads
     with pytest.raises(_lib.MuxError):
         ops.prefill_attention(torch.empty_like(q), q, q, q, cu, 16, 0.0)      # scale must be positive
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_many_short_prompts_fill_every_sm_twice(dtype):
+    """Thousands of short CTAs, two per SM: the hand-offs between warps that run a step apart must hold."""
+    gen = torch.Generator().manual_seed(11)
+    lens = torch.randint(200, 513, (160,), generator=gen).tolist()
+    _run(lens, 8, 8, dtype, 12)
