@@ -175,6 +175,18 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&s)[3
       : "memory");
 }
 
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float a, float b);
 template <>
@@ -213,6 +225,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
   const int seq = blockIdx.z, head = blockIdx.y;
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // the tiles with the most work start first
 
+  if (tid == kKWarp * 32) {  // the copy descriptors do not depend on the previous kernel: fetch them early
+    prefetch_tensormap(&tmq);
+    prefetch_tensormap(&tmk);
+  } else if (tid == kVWarp * 32) {
+    prefetch_tensormap(&tmv);
+  }
   griddep_wait();
   const int start = p.cu_seqlens[seq];
   const int len = p.cu_seqlens[seq + 1] - start;
@@ -251,12 +269,16 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     }
     mbar_init_fence();
   }
-  if (warp == kQkWarp) tmem_alloc(sSlot, kTmemCols);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *slot;
+  __syncthreads();  // barriers are live: the producers start their copies while tensor memory is being allocated
   griddep_launch_dependents();
+  uint32_t tmem = 0;
+  if (warp != kKWarp && warp != kVWarp) {  // the users of tensor memory meet again after the allocation
+    if (warp == kQkWarp) tmem_alloc(sSlot, kTmemCols);
+    tc_fence_before();
+    named_bar_sync(1, kThreads - 64);
+    tc_fence_after();
+    tmem = *slot;
+  }
 
   if (warp == kKWarp) {
     // ------------------------------------------------------------------ TMA producer: Q, then the K steps
@@ -270,14 +292,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         const uint32_t dst = sK + st * kStepBytes;
-        mbar_wait(bar(S_FULL + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);  // Q.K^T of step j - 2
+        mbar_wait_sleepy(bar(S_FULL + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);  // Q.K^T of step j - 2
         mbar_arrive_expect_tx(bar(K_FULL + st), kStepBytes);
         tma_load_3d(dst, &tmk, 0, kvh, start + j * kStep, bar(K_FULL + st));
         tma_load_3d(dst + kSlabBytes, &tmk, 64, kvh, start + j * kStep, bar(K_FULL + st));
       }
       // No copy of this CTA may still be in flight when it ends (matters only after a failed wait).
       for (int j = (n > kStages ? n - kStages : 0); j < n; ++j)
-        mbar_wait(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait_sleepy(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     }
   } else if (warp == kVWarp) {
     // ------------------------------------------------------------------ TMA producer: the V steps
@@ -287,13 +309,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         const uint32_t dst = sV + st * kStepBytes;
-        mbar_wait(bar(PV_DONE + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);  // P.V of step j - 2
+        mbar_wait_sleepy(bar(PV_DONE + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);  // P.V of step j - 2
         mbar_arrive_expect_tx(bar(V_FULL + st), kStepBytes);
         tma_load_3d(dst, &tmv, 0, kvh, start + j * kStep, bar(V_FULL + st));
         tma_load_3d(dst + kSlabBytes, &tmv, 64, kvh, start + j * kStep, bar(V_FULL + st));
       }
       for (int j = (n > kStages ? n - kStages : 0); j < n; ++j)
-        mbar_wait(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait_sleepy(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     }
   } else if (warp == kQkWarp) {
     // ------------------------------------------------------------------ issuer of S = Q K^T
@@ -306,12 +328,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       // K-major slab: rows 128 B apart, 8-row groups 1024 B apart; a 16-element k-step is 32 B inside the
       // swizzled row, the second 64-element slab one slab further.
       const uint64_t dQ = smem_desc(sQ, 16, 1024);
-      mbar_wait(bar(Q_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
+      mbar_wait_sleepy(bar(Q_FULL), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
       for (int j = 0; j < n; ++j) {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        mbar_wait(bar(K_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
-        mbar_wait(bar(PV_DONE + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait_sleepy(bar(K_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait_sleepy(bar(PV_DONE + st), ph ^ 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
         tc_fence_after();
         const uint64_t dK = smem_desc(sK + st * kStepBytes, 16, 1024);
 #pragma unroll
@@ -332,8 +354,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       for (int j = 0; j < n; ++j) {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        mbar_wait(bar(V_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
-        mbar_wait(bar(P_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait_sleepy(bar(V_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_wait_sleepy(bar(P_FULL + st), ph, p.status, MUX_DEV_WAIT_TIMEOUT);
         tc_fence_after();
         // MN-major slab of V: 64 d-elements contiguous (128 B), 8-token groups 1024 B apart (stride offset),
         // the other 64 d-elements one slab further (leading offset); a k-step is 16 tokens = 2048 B.
@@ -442,23 +464,33 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     __syncwarp();
     tc_fence_after();
     const float inv = 1.f / l_run;
-    const bool valid = qt * kTile + row < len;
-    T* orow = static_cast<T*>(p.out) + (int64_t)(start + qt * kTile + row) * p.out_seq_stride +
-              (int64_t)head * p.out_head_stride;
+    // O / l goes through shared memory (Q's tile: every MMA that read it has completed) so that global memory
+    // is written two whole rows per instruction instead of 32 scattered 16-byte pieces.  Row r keeps its 16
+    // pieces at piece ^ (r % 8): writes (lane = row) and reads (16 lanes = one row) both hit 8 bank groups.
+    const uint32_t srow = sQ + (uint32_t)row * 256u;
 #pragma unroll 1
     for (int c4 = 0; c4 < 4; ++c4) {
       float o[32];
       tmem_ld32<0>(tO + c4 * 32, o);
       tmem_wait_ld();
-      if (valid) {
 #pragma unroll
-        for (int v8 = 0; v8 < 4; ++v8) {
-          uint4 w;
-          w.x = pack_pair<T>(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv);
-          w.y = pack_pair<T>(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
-          w.z = pack_pair<T>(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv);
-          w.w = pack_pair<T>(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
-          *reinterpret_cast<uint4*>(orow + c4 * 32 + v8 * 8) = w;
+      for (int v8 = 0; v8 < 4; ++v8)
+        sts128(srow + (uint32_t)(((c4 * 4 + v8) ^ (row & 7)) << 4),
+               pack_pair<T>(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv), pack_pair<T>(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv),
+               pack_pair<T>(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv), pack_pair<T>(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv));
+    }
+    __syncwarp();  // a warp writes out only the 32 rows it staged itself
+    {
+      const int piece = lane & 15;
+      T* obase = static_cast<T*>(p.out) + (int64_t)(start + qt * kTile) * p.out_seq_stride +
+                 (int64_t)head * p.out_head_stride + piece * 8;
+      const int rows_valid = len - qt * kTile;  // rows of this tile inside the prompt
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int r = warp * 32 + 2 * i + (lane >> 4);
+        if (r < rows_valid) {
+          const uint4 w = lds128(sQ + (uint32_t)r * 256u + (uint32_t)((piece ^ (r & 7)) << 4));
+          *reinterpret_cast<uint4*>(obase + (int64_t)r * p.out_seq_stride) = w;
         }
       }
     }

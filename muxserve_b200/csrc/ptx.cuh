@@ -69,6 +69,33 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, unsigne
   atomicOr(status, timeout_bit);
 }
 
+// The same bounded wait for threads that expect to wait long (a producer or an MMA-issuing thread of the
+// prompt kernel): each poll carries a suspend-time hint, so the thread sleeps in hardware until the phase
+// completes or the hint (in ns) runs out instead of spinning through the issue slots of its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+constexpr uint32_t kSleepyHintNs = 2000;
+constexpr uint32_t kSleepyLimit = 1u << 18;  // x 2 us: the same order of patience as kWaitLimit spins
+
+__device__ __forceinline__ void mbar_wait_sleepy(uint32_t bar, uint32_t parity, unsigned* status,
+                                                 unsigned timeout_bit) {
+  for (uint32_t i = 0; i < kSleepyLimit; ++i) {
+    if (mbar_try_wait_hint(bar, parity, kSleepyHintNs)) return;
+    if ((i & 15u) == 15u && (*reinterpret_cast<volatile unsigned*>(status) & timeout_bit)) return;
+  }
+  atomicOr(status, timeout_bit);
+}
+
 // 1-D bulk copy global -> shared of `bytes` (multiple of 16, both sides 16-B
 // aligned), completion counted on `bar`.  Non-multicast.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
