@@ -257,19 +257,41 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
   const uint32_t sSlot = sBar + 8u * NUM_BARS;
   volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem_raw + (sSlot - raw));
 
-  if (tid == 0) {
+  // Each producer lane arms its own barriers and sends its first copies at once (the first kStages steps
+  // need no free-stage signal); everybody else meets them at the CTA barrier below.
+  const int kvh = head / p.group;
+  const int first = min(n, kStages);
+  if (tid == kKWarp * 32) {
     mbar_init(bar(Q_FULL), 1);
+    for (int i = 0; i < kStages; ++i) mbar_init(bar(K_FULL + i), 1);
+    mbar_init_fence();
+    const int q0 = start + qt * kTile;
+    mbar_arrive_expect_tx(bar(Q_FULL), kQBytes);
+    tma_load_3d(sQ, &tmq, 0, head, q0, bar(Q_FULL));
+    tma_load_3d(sQ + kQSlabBytes, &tmq, 64, head, q0, bar(Q_FULL));
+    for (int j = 0; j < first; ++j) {
+      mbar_arrive_expect_tx(bar(K_FULL + j), kStepBytes);
+      tma_load_3d(sK + j * kStepBytes, &tmk, 0, kvh, start + j * kStep, bar(K_FULL + j));
+      tma_load_3d(sK + j * kStepBytes + kSlabBytes, &tmk, 64, kvh, start + j * kStep, bar(K_FULL + j));
+    }
+  } else if (tid == kVWarp * 32) {
+    for (int i = 0; i < kStages; ++i) mbar_init(bar(V_FULL + i), 1);
+    mbar_init_fence();
+    for (int j = 0; j < first; ++j) {
+      mbar_arrive_expect_tx(bar(V_FULL + j), kStepBytes);
+      tma_load_3d(sV + j * kStepBytes, &tmv, 0, kvh, start + j * kStep, bar(V_FULL + j));
+      tma_load_3d(sV + j * kStepBytes + kSlabBytes, &tmv, 64, kvh, start + j * kStep, bar(V_FULL + j));
+    }
+  } else if (tid == 0) {
     mbar_init(bar(P_FULL), kSoftmaxWarps);
     mbar_init(bar(P_FULL + 1), kSoftmaxWarps);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(bar(K_FULL + i), 1);
-      mbar_init(bar(V_FULL + i), 1);
       mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(PV_DONE + i), 1);
     }
     mbar_init_fence();
   }
-  __syncthreads();  // barriers are live: the producers start their copies while tensor memory is being allocated
+  __syncthreads();  // all barriers are live; tensor memory is allocated while the first copies fly
   griddep_launch_dependents();
   uint32_t tmem = 0;
   if (warp != kKWarp && warp != kVWarp) {  // the users of tensor memory meet again after the allocation
@@ -281,14 +303,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
   }
 
   if (warp == kKWarp) {
-    // ------------------------------------------------------------------ TMA producer: Q, then the K steps
+    // ------------------------------------------------------------------ TMA producer: the later K steps
     if (lane == 0) {
-      const int kvh = head / p.group;
-      const int q0 = start + qt * kTile;
-      mbar_arrive_expect_tx(bar(Q_FULL), kQBytes);
-      tma_load_3d(sQ, &tmq, 0, head, q0, bar(Q_FULL));
-      tma_load_3d(sQ + kQSlabBytes, &tmq, 64, head, q0, bar(Q_FULL));
-      for (int j = 0; j < n; ++j) {
+      for (int j = first; j < n; ++j) {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         const uint32_t dst = sK + st * kStepBytes;
@@ -302,10 +319,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         mbar_wait_sleepy(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
     }
   } else if (warp == kVWarp) {
-    // ------------------------------------------------------------------ TMA producer: the V steps
+    // ------------------------------------------------------------------ TMA producer: the later V steps
     if (lane == 0) {
-      const int kvh = head / p.group;
-      for (int j = 0; j < n; ++j) {
+      for (int j = first; j < n; ++j) {
         const int st = j & 1;
         const uint32_t ph = (uint32_t)(j >> 1) & 1u;
         const uint32_t dst = sV + st * kStepBytes;
