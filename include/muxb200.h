@@ -298,7 +298,16 @@ typedef struct {
   int32_t num_kv_heads;
   int32_t head_size;
   int32_t dtype;
-  int32_t reserved;
+  int32_t block_size;        /* of the pool below; ignored when key_cache is NULL */
+  /* Optional: the prompt-phase cache write in the same launch.  When key_cache is not NULL every K/V row is also
+   * written to its slot, exactly as mux_reshape_and_cache(k, v, ..., slot_mapping) would (negative slot = skip the
+   * row, slot outside the pool = MUX_DEV_BAD_SLOT and skipped): the CTA that holds a K/V step of its own query
+   * rows in shared memory copies it to the pool while the attention of the last steps runs. */
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping;   /* device, [total_tokens, num_kv_heads] by the two strides (elements) */
+  int64_t slot_token_stride, slot_head_stride;
+  int64_t num_blocks;
 } mux_prefill_args_t;
 
 int mux_prefill_attention(const mux_prefill_args_t* args, void* cuda_stream);

@@ -21,7 +21,7 @@ MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 MUX_DEV_INTERNAL = 32
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 
 class CacheWriteArgs(C.Structure):
@@ -113,7 +113,9 @@ class PrefillArgs(C.Structure):
         ("cu_seqlens", C.c_void_p), ("scale", C.c_float),
         ("num_seqs", C.c_int32), ("total_tokens", C.c_int32), ("max_prompt_len", C.c_int32),
         ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_size", C.c_int32),
-        ("dtype", C.c_int32), ("reserved", C.c_int32),
+        ("dtype", C.c_int32), ("block_size", C.c_int32),
+        ("key_cache", C.c_void_p), ("value_cache", C.c_void_p), ("slot_mapping", C.c_void_p),
+        ("slot_token_stride", C.c_int64), ("slot_head_stride", C.c_int64), ("num_blocks", C.c_int64),
     ]
 
 

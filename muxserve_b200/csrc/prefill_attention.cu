@@ -56,14 +56,20 @@ struct Params {
   void* out;
   int64_t out_seq_stride, out_head_stride;  // elements
   const int32_t* cu_seqlens;                // [num_seqs + 1]
- int total_tokens;
+  int total_tokens;
   int max_prompt_len;
   int group;                                // q heads per kv head
   float scale_log2;                         // scale * log2(e)
   unsigned* status;
+  // optional cache write of the K/V rows (kc == nullptr: none)
+  void* kc;
+  void* vc;
+  const long long* slots;
+  long long s_ts, s_hs, num_blocks;
+  int block_size;
 };
 
-constexpr int smem_bytes() { return kQBytes + 2 * kStages * kStepBytes + 1024; }  // a multiple of 1024
+constexpr int smem_bytes() { return kQBytes + 2 * kStages * kStepBytes + 2048; }  // tiles + barriers + 128 slots
 
 // ---- tcgen05 / TMA building blocks -----------------------------------------------------------
 
@@ -183,6 +189,15 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr)
+               : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -199,6 +214,109 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
+
+// ---- prompt cache write from the staged steps ------------------------------------------------
+// The CTA of query tile qt holds the K and V steps 2 qt and 2 qt + 1 (its own rows' tokens) in shared memory at
+// the end of its walk; the q head that comes first in its group copies them to the pool: the two producer warps,
+// idle by then, do it while the softmax and the MMAs of those last steps run.
+
+// Slot of the token in row r of step j for this kv head, or -1 (row past the prompt, padding slot, slot outside
+// the pool: reported and skipped).
+__device__ __forceinline__ long long step_slot(const Params& p, int start, int len, int kvh, int j, int r) {
+  const int pos = j * kStep + r;
+  if (pos >= len) return -1;
+  const long long slot = p.slots[(long long)(start + pos) * p.s_ts + (long long)kvh * p.s_hs];
+  if (slot < 0) return -1;
+  if (slot / p.block_size >= p.num_blocks) {
+    atomicOr(p.status, MUX_DEV_BAD_SLOT);
+    return -1;
+  }
+  return slot;
+}
+
+// K step (64 tokens x 128 d, two 128-byte-swizzled slabs) -> key pool [block][d/8][token][8]: lane = row, one
+// 16-byte piece per d chunk; consecutive tokens of a block are neighbouring pieces.  `slots`: the step's 64
+// slots in shared memory (fetched at the start of the CTA: the [token][layer][head] array puts consecutive
+// tokens kilobytes apart, and a fetch at the point of use would stall the copy for a DRAM round trip each time).
+template <typename T>
+__device__ __forceinline__ void copy_k_step(const Params& p, uint32_t tile, const long long* slots, int lane) {
+  const int BS = p.block_size;
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    const int r = half * 32 + lane;
+    const long long slot = slots[r];
+    if (slot < 0) continue;
+    const long long blk = slot / BS;
+    T* dst = static_cast<T*>(p.kc) + blk * (128 * BS) + (slot - blk * BS) * 8;
+    const uint32_t src = tile + (uint32_t)r * 128u;
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {
+      const uint4 w = lds128(src + (uint32_t)(c >> 3) * kSlabBytes + (uint32_t)(((c & 7) ^ (r & 7)) << 4));
+      *reinterpret_cast<uint4*>(dst + c * (BS * 8)) = w;
+    }
+  }
+}
+
+// V step -> value pool [block][d][token], groups g0 .. g1 - 1 of eight tokens each.  Eight tokens whose slots are
+// consecutive and start on a multiple of 8 (every full group of a prompt) are transposed by ldmatrix.trans:
+// per 8 x 8 piece a lane gets two neighbouring tokens of one d, i.e. 4 bytes of that d's row in the block, and
+// four lanes complete its 16 bytes.  Other rows go element by element.
+template <typename T>
+__device__ __forceinline__ void copy_v_groups(const Params& p, uint32_t tile, const long long* slots, int lane, int g0,
+                                              int g1) {
+  const int BS = p.block_size;
+  const long long slot_a = slots[lane];        // rows 0..31
+  const long long slot_b = slots[32 + lane];   // rows 32..63
+  unsigned short* vc = reinterpret_cast<unsigned short*>(p.vc);
+#pragma unroll 1
+  for (int g = g0; g < g1; ++g) {  // rows 8 g .. 8 g + 7
+    const long long mine = g < 4 ? slot_a : slot_b;
+    const int l0 = (g & 3) * 8;
+    const long long base = __shfl_sync(0xffffffffu, mine, l0);
+    const bool in_group = (lane >> 3) == (g & 3);
+    const unsigned good = __ballot_sync(0xffffffffu, in_group && mine >= 0 && mine == base + (lane & 7));
+    const bool run = base >= 0 && (base & 7) == 0 && ((good >> l0) & 0xffu) == 0xffu;
+    const int r0 = g * 8;
+    if (run) {
+      const long long blk = base / BS;
+      // this lane's destination inside a piece: d = lane / 4 of the piece, tokens 2 (lane % 4), + 1
+      unsigned short* dst = vc + blk * (128 * BS) + (base - blk * BS) + (long long)(lane >> 2) * BS + 2 * (lane & 3);
+      const int r = r0 + (lane & 7);  // the row whose 16-byte piece this lane names to ldmatrix
+      const uint32_t rowaddr = tile + (uint32_t)r * 128u;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {  // pieces (d chunks) 4 q4 .. 4 q4 + 3, one per lane octet
+        const int c = 4 * q4 + (lane >> 3);
+        uint32_t m[4];
+        ldmatrix_x4_trans(m, rowaddr + (uint32_t)(c >> 3) * kSlabBytes + (uint32_t)(((c & 7) ^ (r & 7)) << 4));
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint32_t*>(dst + (long long)(8 * (4 * q4 + i)) * BS) = m[i];
+      }
+    } else {
+#pragma unroll 1
+      for (int i = 0; i < 8; ++i) {
+        const long long slot = __shfl_sync(0xffffffffu, mine, l0 + i);
+        if (slot < 0) continue;  // the same for every lane
+        const int r = r0 + i;
+        const long long blk = slot / BS;
+        unsigned short* dst = vc + blk * (128 * BS) + (slot - blk * BS);
+#pragma unroll 1
+        for (int pass = 0; pass < 4; ++pass) {
+          const int d = pass * 32 + lane;
+          unsigned short x;
+          asm volatile("ld.shared.u16 %0, [%1];"
+                       : "=h"(x)
+                       : "r"(tile + (uint32_t)(d >> 6) * kSlabBytes + (uint32_t)r * 128u +
+                             (uint32_t)((((d & 63) >> 3) ^ (r & 7)) << 4) + (uint32_t)(d & 7) * 2u)
+                       : "memory");
+          dst[(long long)d * BS] = x;
+        }
+      }
+    }
+  }
+}
+
+constexpr int kVGroupsOfVWarp = 5;  // of the 8 groups of a step; the K warp, which also copies K, takes the rest
 
 // ---- the kernel ------------------------------------------------------------------------------
 //
@@ -260,6 +378,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
   // Each producer lane arms its own barriers and sends its first copies at once (the first kStages steps
   // need no free-stage signal); everybody else meets them at the CTA barrier below.
   const int kvh = head / p.group;
+  const bool write_pool = p.kc != nullptr && head % p.group == 0;
   const int first = min(n, kStages);
   if (tid == kKWarp * 32) {
     mbar_init(bar(Q_FULL), 1);
@@ -302,6 +421,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     tmem = *slot;
   }
 
+  long long* sslots = reinterpret_cast<long long*>(smem_raw + (sBar + 256 - raw));  // [2 steps][64 rows]
+  if (write_pool && (warp == kKWarp || warp == kVWarp) && lane > 0) {
+    // the idle lanes of the producer warps fetch the slots of this tile's 128 tokens (K warp: step 2 qt, V warp:
+    // step 2 qt + 1) while the first copies are in flight
+    const int which = warp == kKWarp ? 0 : 1;
+    for (int r = lane - 1; r < kStep; r += 31)
+      sslots[which * kStep + r] = step_slot(p, start, len, kvh, first_masked + which, r);
+  }
   if (warp == kKWarp) {
     // ------------------------------------------------------------------ TMA producer: the later K steps
     if (lane == 0) {
@@ -314,9 +441,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         tma_load_3d(dst, &tmk, 0, kvh, start + j * kStep, bar(K_FULL + st));
         tma_load_3d(dst + kSlabBytes, &tmk, 64, kvh, start + j * kStep, bar(K_FULL + st));
       }
-      // No copy of this CTA may still be in flight when it ends (matters only after a failed wait).
-      for (int j = (n > kStages ? n - kStages : 0); j < n; ++j)
-        mbar_wait_sleepy(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+    }
+    __syncwarp();
+    if (write_pool) named_bar_sync(4, 64);  // both producer warps: all 128 slots are in shared memory
+    // The last steps: no copy of this CTA may still be in flight when it ends (matters only after a failed
+    // wait), and the steps of this tile's own tokens (2 qt and 2 qt + 1, never overwritten) go to the pool.
+    for (int j = (n > kStages ? n - kStages : 0); j < n; ++j) {
+      mbar_wait_sleepy(bar(K_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+      __syncwarp();
+      if (write_pool && j >= first_masked) {
+        copy_k_step<T>(p, sK + (j & 1) * kStepBytes, sslots + (j - first_masked) * kStep, lane);
+        named_bar_sync(2 + (j & 1), 64);  // the V warp has seen this step's V land (one barrier per step: its 32
+                                          // arrivals and this warp's 32 make 64 whichever side comes first)
+        copy_v_groups<T>(p, sV + (j & 1) * kStepBytes, sslots + (j - first_masked) * kStep, lane, kVGroupsOfVWarp, 8);
+      }
     }
   } else if (warp == kVWarp) {
     // ------------------------------------------------------------------ TMA producer: the later V steps
@@ -330,8 +468,16 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
         tma_load_3d(dst, &tmv, 0, kvh, start + j * kStep, bar(V_FULL + st));
         tma_load_3d(dst + kSlabBytes, &tmv, 64, kvh, start + j * kStep, bar(V_FULL + st));
       }
-      for (int j = (n > kStages ? n - kStages : 0); j < n; ++j)
-        mbar_wait_sleepy(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+    }
+    __syncwarp();
+    if (write_pool) named_bar_sync(4, 64);
+    for (int j = (n > kStages ? n - kStages : 0); j < n; ++j) {
+      mbar_wait_sleepy(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+      __syncwarp();
+      if (write_pool && j >= first_masked) {
+        named_bar_arrive(2 + (j & 1), 64);  // lets the K warp take its share of this step's V
+        copy_v_groups<T>(p, sV + (j & 1) * kStepBytes, sslots + (j - first_masked) * kStep, lane, 0, kVGroupsOfVWarp);
+      }
     }
   } else if (warp == kQkWarp) {
     // ------------------------------------------------------------------ issuer of S = Q K^T
@@ -608,6 +754,12 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
   if (!stride_ok(a->out_seq_stride, a->out_head_stride) || !stride_ok(a->q_seq_stride, a->q_head_stride) ||
       !stride_ok(a->k_seq_stride, a->k_head_stride) || !stride_ok(a->v_seq_stride, a->v_head_stride))
     return MUX_ERR_MISALIGNED;
+  if (a->key_cache != nullptr) {
+    if (a->block_size != 8 && a->block_size != 16 && a->block_size != 32) return MUX_ERR_BAD_BLOCK_SIZE;
+    if (!a->value_cache || !a->slot_mapping) return MUX_ERR_NULL_POINTER;
+    if (a->num_blocks <= 0) return MUX_ERR_BAD_SHAPE;
+    if (!aligned16(a->key_cache) || !aligned16(a->value_cache)) return MUX_ERR_MISALIGNED;
+  }
   unsigned* status = device_status_ptr();
   if (status == nullptr) return MUX_ERR_CUDA;
   EncodeTiledFn enc = nullptr;
@@ -628,6 +780,13 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
   prm.group = a->num_q_heads / a->num_kv_heads;
   prm.scale_log2 = a->scale * 1.4426950408889634f;
   prm.status = status;
+  prm.kc = a->key_cache;
+  prm.vc = a->value_cache;
+  prm.slots = reinterpret_cast<const long long*>(a->slot_mapping);
+  prm.s_ts = a->slot_token_stride;
+  prm.s_hs = a->slot_head_stride;
+  prm.num_blocks = a->num_blocks;
+  prm.block_size = a->block_size;
   if (a->dtype == MUX_DTYPE_F16) return launch<__half, false>(a, mq, mk, mv, prm, stream);
   return launch<__nv_bfloat16, true>(a, mq, mk, mv, prm, stream);
 }

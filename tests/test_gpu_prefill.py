@@ -96,3 +96,55 @@ def test_many_short_prompts_fill_every_sm_twice(dtype):
     gen = torch.Generator().manual_seed(11)
     lens = torch.randint(200, 513, (160,), generator=gen).tolist()
     _run(lens, 8, 8, dtype, 12)
+
+
+# ---- prompt cache write in the same launch ----------------------------------------------------------------
+def _fused_case(lens, Hq, H, dtype, B, seed, spoil=False):
+    from muxserve_b200 import flexstore, ops, workloads
+    from oracle.cache_write_oracle import reshape_and_cache_ref
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(seed)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    T, L, nblk = int(lens_t.sum()), 2, 4096
+    tables, _ = workloads.scatter_block_tables(lens_t, L, H, B, torch.randperm(nblk, generator=gen).to(dev))
+    slots = workloads.prompt_slots(tables, lens_t, B)                     # [T, L, H]; the op gets the layer-1 slice
+    if spoil:
+        slots[3, 1, 0] = -1                                               # padding row: skipped
+        slots[T - 2, 1, H - 1] = nblk * B + 5                             # outside the pool: reported and skipped
+        slots[40:48, 1, 0] = slots[40:48, 1, 0].flip(0)                   # a group of 8 that is not a run
+    q = torch.randn((T, Hq, 128), generator=gen).to(dtype).to(dev)
+    k = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    v = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    kc, vc = flexstore.allocate_gpu_cache(nblk, B, dtype, dev)
+    workloads.fill_pool_(kc, vc, seed + 1)
+    kc_c, vc_c = kc.cpu().clone(), vc.cpu().clone()
+    out = torch.full((T, Hq, 128), float("nan"), dtype=dtype, device=dev)
+    cu = ops.cu_seqlens_from_prompt_lens(lens, dev)
+    ops.prefill_attention(out, q, k, v, cu, max(lens), 128 ** -0.5, key_cache=kc, value_cache=vc,
+                          slot_mapping=slots[:, 1, :])
+    torch.cuda.synchronize()
+    status = ops.device_status()
+    ok = slots[:, 1, :].cpu().clone()
+    ok[ok >= nblk * B] = -1
+    reshape_and_cache_ref(k.cpu(), v.cpu(), kc_c, vc_c, ok)
+    assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16)), "key pool differs"
+    assert torch.equal(vc.cpu().view(torch.int16), vc_c.view(torch.int16)), "value pool differs"
+    ref = prefill_attention_ref(q, k, v, lens, 128 ** -0.5)
+    err = (out.float().cpu() - ref).abs()
+    assert (err <= ATOL + RTOL * ref.abs()).all()
+    return status
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B", [8, 16, 32])
+def test_fused_prompt_cache_write_bit_exact(dtype, B):
+    assert _fused_case([1, 7, 64, 100, 129, 300, 515], 4, 4, dtype, B, 21 + B) == 0
+
+
+def test_fused_prompt_cache_write_gqa_writes_each_kv_head_once():
+    assert _fused_case([33, 260, 513, 128], 8, 2, torch.bfloat16, 16, 31) == 0
+
+
+def test_fused_prompt_cache_write_padding_bad_slots_and_broken_runs():
+    from muxserve_b200 import _lib
+    assert _fused_case([200, 90], 2, 2, torch.float16, 16, 41, spoil=True) == _lib.MUX_DEV_BAD_SLOT
