@@ -77,6 +77,47 @@ def test_validation_happens_before_any_launch(built_lib):
     assert b"16-byte" in L.mux_strerror(-5)
 
 
+def test_prefill_validation_and_struct_layout(built_lib):
+    import subprocess, tempfile
+    from muxserve_b200 import _lib
+    L = built_lib
+    src = f'#include <stdio.h>\n#include <stddef.h>\n#include "{ROOT}/include/muxb200.h"\nint main(){{printf("%zu %zu %zu\\n", ' \
+          'sizeof(mux_prefill_args_t), offsetof(mux_prefill_args_t, cu_seqlens), offsetof(mux_prefill_args_t, key_cache));return 0;}'
+    with tempfile.TemporaryDirectory() as d:
+        (Path(d) / "s.c").write_text(src)
+        subprocess.run(["gcc", "-o", f"{d}/s", f"{d}/s.c"], check=True)
+        got = [int(x) for x in subprocess.run([f"{d}/s"], capture_output=True, text=True, check=True).stdout.split()]
+    P = _lib.PrefillArgs
+    assert got == [C.sizeof(P), P.cu_seqlens.offset, P.key_cache.offset]
+    a = P()
+    assert L.mux_prefill_attention(None, None) == -1
+    a.dtype, a.head_size = 3, 128
+    assert L.mux_prefill_attention(C.byref(a), None) == -2                 # dtype
+    a.dtype, a.head_size = 1, 96
+    assert L.mux_prefill_attention(C.byref(a), None) == -3                 # head size
+    a.head_size, a.num_seqs, a.total_tokens, a.max_prompt_len, a.num_q_heads, a.num_kv_heads = 128, 2, 64, 40, 6, 4
+    a.scale = 0.1
+    assert L.mux_prefill_attention(C.byref(a), None) == -7                 # 6 q heads over 4 kv heads
+    a.num_kv_heads, a.scale = 3, 0.0
+    assert L.mux_prefill_attention(C.byref(a), None) == -6                 # scale must be positive
+    a.scale = 0.1
+    assert L.mux_prefill_attention(C.byref(a), None) == -1                 # null tensors
+    for f in ("out", "q", "k", "v", "cu_seqlens"):
+        setattr(a, f, 0x4000)
+    for f in ("out", "q", "k", "v"):
+        setattr(a, f + "_seq_stride", 6 * 128)
+        setattr(a, f + "_head_stride", 128)
+    a.k_head_stride = 100
+    assert L.mux_prefill_attention(C.byref(a), None) == -5                 # rows must start on 16-byte boundaries
+    a.k_head_stride, a.key_cache, a.block_size = 128, 0x8000, 12
+    assert L.mux_prefill_attention(C.byref(a), None) == -4                 # pool block size
+    a.block_size = 16
+    assert L.mux_prefill_attention(C.byref(a), None) == -1                 # value pool / slots missing
+    a.num_seqs = 0
+    a.key_cache = None
+    assert L.mux_prefill_attention(C.byref(a), None) == 0                  # nothing to do: no launch, no CUDA call
+
+
 def test_ops_refuse_cpu_tensors(built_lib):
     import torch
     from muxserve_b200 import ops
