@@ -1,4 +1,4 @@
-"""CPU oracle of the decode attention path.  TEST INFRASTRUCTURE ONLY.
+"""CPU oracle of the attention path (decode and prompt phase).  TEST INFRASTRUCTURE ONLY.
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs
 of ``bench.py`` may import this package; nothing under ``muxserve_b200/`` does.
@@ -18,4 +18,7 @@ Pinning status
   algorithm (vLLM paged attention) on the pool layout the reference defines
   (muxserve/flexstore/manager.py:456-468) and the slot formula of
   csrc/batch_scheduler.h:42-67.
+* rotary embedding and prompt-phase attention (``rotary_oracle.py``, ``prefill_oracle.py``):
+  PARITY UNPINNED for the same reason (the prompt branch and the rotary step are inside
+  the fork's ``PagedAttentionWithRoPE``); both restate the published semantics in fp32.
 """
