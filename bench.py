@@ -53,6 +53,24 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 1204517000 + 12780544}
 
 
+_JSON_OUT = None
+
+
+def claim_stdout():
+    """Keeps the process's stdout for the ONE JSON line: native libraries write there too (NCCL prints its
+    version banner to fd 1), so fd 1 is pointed at stderr and the line goes out through a saved duplicate."""
+    global _JSON_OUT
+    if _JSON_OUT is None:
+        sys.stdout.flush()
+        _JSON_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _JSON_OUT if _JSON_OUT is not None else sys.stdout
+    print(json.dumps(line), file=out, flush=True)
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -239,7 +257,7 @@ def run_reference(args):
         "e2e": {"value": tokens_per_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference ships no CPU (or CUDA) source for these ops; this arm is the oracle port",
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------- native arm
@@ -570,7 +588,7 @@ def run_native(args):
             line["two_op"] = two_op
         if tp is not None:
             line["tp"] = tp
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -721,7 +739,7 @@ def run_native_c3(args):
             "cpu_baseline": None, "e2e": None, "gpu_launches": gpu_launches, "clocks": clocks, "device_status": status,
             "eager_ms_per_step": ms_eager,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -905,7 +923,7 @@ def run_native_prefill(args):
                            "d2h_bytes_per_step": last_h.numel() * last_h.element_size()}
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = prefill_cpu_baseline(w, lens, args)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -936,6 +954,7 @@ def prefill_cpu_baseline(w, lens, args):
 
 def main():
     args = parse_args()
+    claim_stdout()
     if args.impl == "reference":
         if args.workload in ("c3", "prefill"):
             raise SystemExit("--impl reference supports c2, c4, c5")
