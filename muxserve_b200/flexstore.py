@@ -43,3 +43,37 @@ def allocate_gpu_cache(num_blocks: int, block_size: int, dtype: torch.dtype = to
     k = torch.empty((num_blocks, *get_key_block_shape(block_size, es)), dtype=dtype, device=device)
     v = torch.empty((num_blocks, *get_value_block_shape(block_size)), dtype=dtype, device=device)
     return k, v
+
+
+def get_tensor_metadata(tensor: torch.Tensor) -> dict:
+    """Everything another process on the same GPU needs to map ``tensor`` through CUDA IPC — the dictionary the
+    FlexStore service sends to its model workers for pool and weight tensors
+    (muxserve/flexstore/manager.py:893-911, same keys).  The exporting process must keep ``tensor`` alive."""
+    if not tensor.is_cuda:
+        raise RuntimeError("only CUDA tensors can be exported through CUDA IPC")
+    storage = tensor._typed_storage()
+    (device, handle, size_bytes, offset_bytes, ref_counter_handle, ref_counter_offset, event_handle,
+     event_sync_required) = storage._share_cuda_()
+    return {
+        "tensor_size": tensor.size(),
+        "tensor_stride": tensor.stride(),
+        "tensor_offset": tensor.storage_offset(),
+        "storage_cls": type(storage),
+        "dtype": tensor.dtype,
+        "storage_device": device,
+        "storage_handle": handle,
+        "storage_size_bytes": size_bytes,
+        "storage_offset_bytes": offset_bytes,
+        "requires_grad": tensor.requires_grad,
+        "ref_counter_handle": ref_counter_handle,
+        "ref_counter_offset": ref_counter_offset,
+        "event_handle": event_handle,
+        "event_sync_required": event_sync_required,
+    }
+
+
+def rebuild_tensor(metadata: dict) -> torch.Tensor:
+    """The importing side: a tensor over the exporter's memory (what the worker does with each received dictionary,
+    muxserve/flexserver/model_loader.py:44-49)."""
+    from torch.multiprocessing.reductions import rebuild_cuda_tensor
+    return rebuild_cuda_tensor(torch.Tensor, **metadata)
