@@ -870,17 +870,27 @@ def run_native_prefill(args):
     # slot mapping) goes up from pinned memory, the last-token rows the sampler reads come back
     cu_h = cu.cpu().pin_memory()
     slots_h = slots.cpu().pin_memory()
+    tables_h = tables.cpu().pin_memory()
     last_rows = (cu[1:].long() - 1)
     last_h = torch.empty((S, Hq, 128), dtype=dt).pin_memory()
-    cu_d, slots_d = torch.empty_like(cu), torch.empty_like(slots)
+    cu_d, slots_d, tables_d = torch.empty_like(cu), torch.empty_like(slots), torch.empty_like(tables)
 
-    def e2e_step():
+    def e2e_step():      # the reference's hand-over: the [T, L, H] int64 slot mapping goes up every step
         cu_d.copy_(cu_h, non_blocking=True)
         slots_d.copy_(slots_h, non_blocking=True)
         for l in range(L):
             i = l % Lq
             ops.prefill_attention(out, q[i], k[i], v[i], cu_d, max_len, scale, key_cache=kc, value_cache=vc,
                                   slot_mapping=slots_d[:, l, :])
+        last_h.copy_(out[last_rows], non_blocking=True)
+
+    def e2e_step_tables():   # the prompts' block lists [L, S, H, max_blocks] int32 go up instead
+        cu_d.copy_(cu_h, non_blocking=True)
+        tables_d.copy_(tables_h, non_blocking=True)
+        for l in range(L):
+            i = l % Lq
+            ops.prefill_attention(out, q[i], k[i], v[i], cu_d, max_len, scale, key_cache=kc, value_cache=vc,
+                                  block_tables=tables_d[l])
         last_h.copy_(out[last_rows], non_blocking=True)
 
     e2e = None
@@ -894,10 +904,20 @@ def run_native_prefill(args):
         e1.record(stream)
         barrier()
         e2e_ms = e0.elapsed_time(e1) / args.steps
-    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, att], dtype=torch.float64, device=dev)
+        for _ in range(3):
+            e2e_step_tables()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step_tables()
+        e1.record(stream)
+        barrier()
+        e2e_tables_ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, att, e2e_tables_ms if not args.no_e2e else 0.0],
+                     dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, att = (float(x) for x in t)
+    ms, e2e_ms, att, e2e_tables_ms = (float(x) for x in t)
     if rank == 0:
         flops = workloads.prefill_flops(lens.tolist(), Hq)
         peak, peak_src = tensor_peak()
@@ -920,7 +940,10 @@ def run_native_prefill(args):
         if not args.no_e2e:
             line["e2e"] = {"value": T * world / (e2e_ms * 1e-3), "unit": "tokens/s",
                            "h2d_bytes_per_step": cu_h.numel() * 4 + slots_h.numel() * 8,
-                           "d2h_bytes_per_step": last_h.numel() * last_h.element_size()}
+                           "d2h_bytes_per_step": last_h.numel() * last_h.element_size(),
+                           "with_block_tables": {"value": T * world / (e2e_tables_ms * 1e-3), "unit": "tokens/s",
+                                                 "h2d_bytes_per_step": cu_h.numel() * 4 + tables_h.numel() * 4,
+                                                 "note": "block lists uploaded instead of the slot mapping"}}
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = prefill_cpu_baseline(w, lens, args)
         emit(line)

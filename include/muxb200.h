@@ -305,9 +305,17 @@ typedef struct {
    * rows in shared memory copies it to the pool while the attention of the last steps runs. */
   void* key_cache;
   void* value_cache;
-  const int64_t* slot_mapping;   /* device, [total_tokens, num_kv_heads] by the two strides (elements) */
+  const int64_t* slot_mapping;   /* device, [total_tokens, num_kv_heads] by the two strides (elements), or NULL */
   int64_t slot_token_stride, slot_head_stride;
   int64_t num_blocks;
+  /* Instead of slot_mapping (used when slot_mapping is NULL): this layer's block lists, as the decode ops take
+   * them.  Token t of prompt i, kv head h goes to slot block_tables[i][h][t / block_size] * block_size +
+   * t % block_size — the slots getPromptSlots (csrc/batch_scheduler.h:42-56) would have listed, without the
+   * [tokens, layers, heads] int64 array.  A negative block id skips the tokens of that block. */
+  const int32_t* block_tables;   /* device, [num_seqs, num_kv_heads, max_blocks] by the two strides (elements) */
+  int64_t bt_seq_stride, bt_head_stride;
+  int32_t max_blocks_per_seq;
+  int32_t reserved;
 } mux_prefill_args_t;
 
 int mux_prefill_attention(const mux_prefill_args_t* args, void* cuda_stream);

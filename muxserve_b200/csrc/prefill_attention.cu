@@ -67,6 +67,9 @@ struct Params {
   const long long* slots;
   long long s_ts, s_hs, num_blocks;
   int block_size;
+  const int* bt;                            // block lists instead of slots (slots == nullptr)
+  long long bt_ss, bt_hs;
+  int max_blocks;
 };
 
 constexpr int smem_bytes() { return kQBytes + 2 * kStages * kStepBytes + 2048; }  // tiles + barriers + 128 slots
@@ -222,10 +225,21 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
 
 // Slot of the token in row r of step j for this kv head, or -1 (row past the prompt, padding slot, slot outside
 // the pool: reported and skipped).
-__device__ __forceinline__ long long step_slot(const Params& p, int start, int len, int kvh, int j, int r) {
+__device__ __forceinline__ long long step_slot(const Params& p, int seq, int start, int len, int kvh, int j, int r) {
   const int pos = j * kStep + r;
   if (pos >= len) return -1;
-  const long long slot = p.slots[(long long)(start + pos) * p.s_ts + (long long)kvh * p.s_hs];
+  long long slot;
+  if (p.slots != nullptr) {
+    slot = p.slots[(long long)(start + pos) * p.s_ts + (long long)kvh * p.s_hs];
+  } else {  // from the block list of (prompt, kv head)
+    const int b = pos / p.block_size;
+    if (b >= p.max_blocks) {
+      atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
+      return -1;
+    }
+    const long long id = p.bt[(long long)seq * p.bt_ss + (long long)kvh * p.bt_hs + b];
+    slot = id < 0 ? -1 : id * p.block_size + (pos - b * p.block_size);
+  }
   if (slot < 0) return -1;
   if (slot / p.block_size >= p.num_blocks) {
     atomicOr(p.status, MUX_DEV_BAD_SLOT);
@@ -427,7 +441,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     // step 2 qt + 1) while the first copies are in flight
     const int which = warp == kKWarp ? 0 : 1;
     for (int r = lane - 1; r < kStep; r += 31)
-      sslots[which * kStep + r] = step_slot(p, start, len, kvh, first_masked + which, r);
+      sslots[which * kStep + r] = step_slot(p, seq, start, len, kvh, first_masked + which, r);
   }
   if (warp == kKWarp) {
     // ------------------------------------------------------------------ TMA producer: the later K steps
@@ -756,7 +770,8 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
     return MUX_ERR_MISALIGNED;
   if (a->key_cache != nullptr) {
     if (a->block_size != 8 && a->block_size != 16 && a->block_size != 32) return MUX_ERR_BAD_BLOCK_SIZE;
-    if (!a->value_cache || !a->slot_mapping) return MUX_ERR_NULL_POINTER;
+    if (!a->value_cache || (!a->slot_mapping && !a->block_tables)) return MUX_ERR_NULL_POINTER;
+    if (!a->slot_mapping && a->max_blocks_per_seq <= 0) return MUX_ERR_BAD_SHAPE;
     if (a->num_blocks <= 0) return MUX_ERR_BAD_SHAPE;
     if (!aligned16(a->key_cache) || !aligned16(a->value_cache)) return MUX_ERR_MISALIGNED;
   }
@@ -787,6 +802,10 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
   prm.s_hs = a->slot_head_stride;
   prm.num_blocks = a->num_blocks;
   prm.block_size = a->block_size;
+  prm.bt = a->block_tables;
+  prm.bt_ss = a->bt_seq_stride;
+  prm.bt_hs = a->bt_head_stride;
+  prm.max_blocks = a->max_blocks_per_seq;
   if (a->dtype == MUX_DTYPE_F16) return launch<__half, false>(a, mq, mk, mv, prm, stream);
   return launch<__nv_bfloat16, true>(a, mq, mk, mv, prm, stream);
 }

@@ -358,15 +358,18 @@ def cu_seqlens_from_prompt_lens(prompt_lens, device) -> torch.Tensor:
 def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                       cu_seqlens: torch.Tensor, max_prompt_len: int, scale: float,
                       key_cache: Optional[torch.Tensor] = None, value_cache: Optional[torch.Tensor] = None,
-                      slot_mapping: Optional[torch.Tensor] = None) -> None:
+                      slot_mapping: Optional[torch.Tensor] = None,
+                      block_tables: Optional[torch.Tensor] = None) -> None:
     """Causal self-attention of every prompt over its own tokens (the prompt branch of PagedAttentionWithRoPE).
 
     ``q``/``out`` [T, Hq(*128)], ``k``/``v`` [T, H(*128)] hold the rows of all prompts back to back;
     ``cu_seqlens`` int32 [S + 1] (device) are the row offsets; ``max_prompt_len`` bounds every prompt length.
     With ``key_cache``/``value_cache``/``slot_mapping`` (int64 [T, H], e.g. ``slot_mapping[:, layer, :]``) the same
-    launch also writes every K/V row to its pool slot, bit for bit what ``reshape_and_cache`` would write."""
+    launch also writes every K/V row to its pool slot, bit for bit what ``reshape_and_cache`` would write.
+    ``block_tables`` (int32 [S, H, max_blocks], this layer's lists as the decode ops take them) may stand in for
+    ``slot_mapping``: token t of a prompt goes to offset ``t % block_size`` of block ``t // block_size`` of its list."""
     _require_cuda(out=out, q=q, k=k, v=v, cu_seqlens=cu_seqlens, key_cache=key_cache, value_cache=value_cache,
-                  slot_mapping=slot_mapping)
+                  slot_mapping=slot_mapping, block_tables=block_tables)
     if cu_seqlens.dtype != torch.int32 or cu_seqlens.dim() != 1 or not cu_seqlens.is_contiguous():
         raise TypeError("cu_seqlens must be a contiguous int32 [num_seqs + 1] tensor")
     code = _dtype_code(q, "q")
@@ -382,18 +385,26 @@ def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: to
     if S < 0:
         raise ValueError("cu_seqlens needs at least one entry")
     pool = dict(block_size=0, key_cache=None, value_cache=None, slot_mapping=None, slot_token_stride=0,
-                slot_head_stride=0, num_blocks=0)
-    if key_cache is not None or value_cache is not None or slot_mapping is not None:
-        if key_cache is None or value_cache is None or slot_mapping is None:
-            raise ValueError("key_cache, value_cache and slot_mapping go together")
+                slot_head_stride=0, num_blocks=0, block_tables=None, bt_seq_stride=0, bt_head_stride=0,
+                max_blocks_per_seq=0, reserved=0)
+    if key_cache is not None or value_cache is not None or slot_mapping is not None or block_tables is not None:
+        if key_cache is None or value_cache is None or (slot_mapping is None) == (block_tables is None):
+            raise ValueError("the cache write needs key_cache, value_cache and ONE of slot_mapping / block_tables")
         nb, bs = _pool(key_cache, value_cache)
         if key_cache.dtype != q.dtype:
             raise TypeError("k/v dtype differs from the pool dtype")
-        if slot_mapping.dtype != torch.int64 or tuple(slot_mapping.shape) != (T, Hk):
-            raise ValueError(f"slot_mapping must be int64 [tokens, kv_heads] = [{T}, {Hk}]")
-        pool = dict(block_size=bs, key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(),
-                    slot_mapping=slot_mapping.data_ptr(), slot_token_stride=slot_mapping.stride(0),
-                    slot_head_stride=slot_mapping.stride(1), num_blocks=nb)
+        pool.update(block_size=bs, key_cache=key_cache.data_ptr(), value_cache=value_cache.data_ptr(), num_blocks=nb)
+        if slot_mapping is not None:
+            if slot_mapping.dtype != torch.int64 or tuple(slot_mapping.shape) != (T, Hk):
+                raise ValueError(f"slot_mapping must be int64 [tokens, kv_heads] = [{T}, {Hk}]")
+            pool.update(slot_mapping=slot_mapping.data_ptr(), slot_token_stride=slot_mapping.stride(0),
+                        slot_head_stride=slot_mapping.stride(1))
+        else:
+            if (block_tables.dtype != torch.int32 or block_tables.dim() != 3 or block_tables.shape[:2] != (S, Hk)
+                    or (block_tables.shape[2] > 1 and block_tables.stride(2) != 1)):
+                raise ValueError(f"block_tables must be int32 [num_seqs, kv_heads, max_blocks] = [{S}, {Hk}, *]")
+            pool.update(block_tables=block_tables.data_ptr(), bt_seq_stride=block_tables.stride(0),
+                        bt_head_stride=block_tables.stride(1), max_blocks_per_seq=block_tables.shape[2])
     args = _lib.PrefillArgs(out=out.data_ptr(), q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(),
                             out_seq_stride=o_ss, out_head_stride=o_hs, q_seq_stride=q_ss, q_head_stride=q_hs,
                             k_seq_stride=k_ss, k_head_stride=k_hs, v_seq_stride=v_ss, v_head_stride=v_hs,

@@ -148,3 +148,34 @@ def test_fused_prompt_cache_write_gqa_writes_each_kv_head_once():
 def test_fused_prompt_cache_write_padding_bad_slots_and_broken_runs():
     from muxserve_b200 import _lib
     assert _fused_case([200, 90], 2, 2, torch.float16, 16, 41, spoil=True) == _lib.MUX_DEV_BAD_SLOT
+
+
+@pytest.mark.parametrize("B", [8, 16, 32])
+def test_fused_prompt_cache_write_from_block_tables(B):
+    """The block lists stand in for the slot mapping: same pool contents as reshape_and_cache with getPromptSlots' slots."""
+    from muxserve_b200 import flexstore, ops, workloads
+    from oracle.cache_write_oracle import reshape_and_cache_ref
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(70 + B)
+    lens = [5, 64, 130, 257, 1]
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    T, L, H, Hq, nblk, dtype = int(lens_t.sum()), 3, 2, 4, 1024, torch.float16
+    tables, _ = workloads.scatter_block_tables(lens_t, L, H, B, torch.randperm(nblk, generator=gen).to(dev))
+    slots = workloads.prompt_slots(tables, lens_t, B)
+    q = torch.randn((T, Hq, 128), generator=gen).to(dtype).to(dev)
+    k = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    v = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    kc, vc = flexstore.allocate_gpu_cache(nblk, B, dtype, dev)
+    workloads.fill_pool_(kc, vc, 3)
+    kc_c, vc_c = kc.cpu().clone(), vc.cpu().clone()
+    out = torch.empty_like(q)
+    ops.prefill_attention(out, q, k, v, ops.cu_seqlens_from_prompt_lens(lens, dev), max(lens), 128 ** -0.5,
+                          key_cache=kc, value_cache=vc, block_tables=tables[2])       # a [S, H, max_blocks] layer slice
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    reshape_and_cache_ref(k.cpu(), v.cpu(), kc_c, vc_c, slots[:, 2, :].cpu())
+    assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
+    assert torch.equal(vc.cpu().view(torch.int16), vc_c.view(torch.int16))
+    ref = prefill_attention_ref(q, k, v, lens, 128 ** -0.5)
+    err = (out.float().cpu() - ref).abs()
+    assert (err <= ATOL + RTOL * ref.abs()).all()
