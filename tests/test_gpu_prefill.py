@@ -179,3 +179,52 @@ def test_fused_prompt_cache_write_from_block_tables(B):
     ref = prefill_attention_ref(q, k, v, lens, 128 ** -0.5)
     err = (out.float().cpu() - ref).abs()
     assert (err <= ATOL + RTOL * ref.abs()).all()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_prefill_fuzz(seed):
+    """Random prompt sets, head layouts, dtypes, block sizes and hand-over forms (none / slot mapping / block lists)."""
+    import random
+    from muxserve_b200 import flexstore, ops, workloads
+    from oracle.cache_write_oracle import reshape_and_cache_ref
+    rng = random.Random(1000 + seed)
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(2000 + seed)
+    dtype = rng.choice([torch.float16, torch.bfloat16])
+    H = rng.choice([1, 2, 3, 4])
+    Hq = H * rng.choice([1, 2, 4])
+    B = rng.choice([8, 16, 32])
+    nprompts = rng.randint(1, 24)
+    lens = [rng.choice([0, 1, rng.randint(2, 63), rng.randint(64, 400), rng.randint(400, 900)]) for _ in range(nprompts)]
+    if sum(lens) == 0:
+        lens[0] = 17
+    mode = rng.choice(["none", "slots", "tables"])
+    scale = rng.choice([128 ** -0.5, 0.05, 0.3])
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    T, L, nblk = int(lens_t.sum()), 2, 2048
+    q = torch.randn((T, Hq, 128), generator=gen).to(dtype).to(dev)
+    k = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    v = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    out = torch.full((T, Hq, 128), float("nan"), dtype=dtype, device=dev)
+    cu = ops.cu_seqlens_from_prompt_lens(lens, dev)
+    kw = {}
+    if mode != "none":
+        tables, _ = workloads.scatter_block_tables(lens_t, L, H, B, torch.randperm(nblk, generator=gen).to(dev))
+        slots = workloads.prompt_slots(tables, lens_t, B)
+        kc, vc = flexstore.allocate_gpu_cache(nblk, B, dtype, dev)
+        workloads.fill_pool_(kc, vc, seed)
+        kc_c, vc_c = kc.cpu().clone(), vc.cpu().clone()
+        kw = dict(key_cache=kc, value_cache=vc)
+        kw.update(slot_mapping=slots[:, 1, :]) if mode == "slots" else kw.update(block_tables=tables[1])
+    ops.prefill_attention(out, q, k, v, cu, max(lens) + rng.choice([0, 0, 77]), scale, **kw)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    ref = prefill_attention_ref(q, k, v, lens, scale)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs()
+    assert (err <= ATOL + RTOL * ref.abs()).all(), f"max err {err.max().item():.3e}"
+    if mode != "none":
+        reshape_and_cache_ref(k.cpu(), v.cpu(), kc_c, vc_c, slots[:, 1, :].cpu())
+        assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
+        assert torch.equal(vc.cpu().view(torch.int16), vc_c.view(torch.int16))
