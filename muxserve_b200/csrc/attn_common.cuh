@@ -51,6 +51,7 @@ struct AttnParams {
   long long kn_s0, kn_s1, vn_s0, vn_s1;  // single model: seq, head strides; mixed: s0 = item (row) stride
   const void* rope_cache;                // fused decode step only: [max_position][64 cos | 64 sin], or nullptr
   long long rope_max_position;
+  long long num_items;                   // (sequence, kv head) items of the launch
 };
 
 // Shared-memory carve-up, identical on host (sizing) and device.

@@ -354,45 +354,78 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   }
 }
 
-// Merges the partitions of every item that has more than one.
+// Merges the partitions of every item that has more than one.  One warp per (item, head tile, q head of the
+// group): the lanes reduce (max, sum) over the partitions, turn them into one weight per partition (kept in shared
+// memory) and then each lane accumulates four output elements from 16-byte loads, eight partitions in flight.
+constexpr int kMergeWarps = 4;
+constexpr int kMergeChunk = 128;  // partitions whose weights are staged at a time
+
 template <typename T, int BS, bool MIXED>
-__global__ void __launch_bounds__(kHeadSize)
+__global__ void __launch_bounds__(kMergeWarps * 32)
 paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
-  __shared__ ItemInfo info;
-  const int item = blockIdx.x, htile = blockIdx.y;
-  const int tid = threadIdx.x;
+  __shared__ ItemInfo infos[kMergeWarps];
+  __shared__ float wts[kMergeWarps][kMergeChunk];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int P = p.pb * BS;
   griddep_wait();
   griddep_launch_dependents();
+  const long long unit = (long long)blockIdx.x * kMergeWarps + warp;
+  if (unit >= p.num_items * p.head_tiles * p.gs) return;
+  const int n = (int)(unit % p.gs);
+  const long long ih = unit / p.gs;
+  const int htile = (int)(ih % p.head_tiles);
+  const int item = (int)(ih / p.head_tiles);
   ItemDesc d = load_item<MIXED>(p, item);
   if (d.ctx < 0) d.ctx = 0;
   if (d.ctx > p.max_context_len) d.ctx = p.max_context_len;
   const int nparts = (d.ctx + P - 1) / P;
   if (nparts <= 1) return;
-  if (tid < 32) resolve_heads<MIXED>(p, d, item, htile, &info, tid);
-  __syncthreads();
-  const int geff = info.geff;
-  T* out = static_cast<T*>(p.out);
+  ItemInfo* info = &infos[warp];
+  resolve_heads<MIXED>(p, d, item, htile, info, lane);
+  __syncwarp();
+  if (n >= info->geff) return;
   const long long slot0 = ((long long)item * p.head_tiles + htile) * p.max_parts;
-  const int lane = tid & 31;
-  for (int n = 0; n < geff; ++n) {
-    // every warp reduces (max, sum) over the partitions with its lanes, so the loads go out together
-    float M = -INFINITY;
-    for (int k = lane; k < nparts; k += 32) M = fmaxf(M, p.ws_ml[((slot0 + k) * p.gs + n) * 2]);
-    M = warp_max(M);
-    float lsum = 0.f;
-    for (int k = lane; k < nparts; k += 32) {
-      const long long r = (slot0 + k) * p.gs + n;
-      lsum += p.ws_ml[r * 2 + 1] * __expf(p.ws_ml[r * 2] - M);
+  float M = -INFINITY;
+  for (int k = lane; k < nparts; k += 32) M = fmaxf(M, p.ws_ml[((slot0 + k) * p.gs + n) * 2]);
+  M = warp_max(M);
+  float lsum = 0.f;
+  for (int k = lane; k < nparts; k += 32) {
+    const long long r = (slot0 + k) * p.gs + n;
+    lsum += p.ws_ml[r * 2 + 1] * __expf(p.ws_ml[r * 2] - M);
+  }
+  lsum = warp_sum(lsum);
+  const float inv = 1.f / lsum;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < nparts; k0 += kMergeChunk) {
+    const int cnt = min(kMergeChunk, nparts - k0);
+    for (int k = lane; k < cnt; k += 32)
+      wts[warp][k] = __expf(p.ws_ml[((slot0 + k0 + k) * p.gs + n) * 2] - M) * inv;
+    __syncwarp();
+    const float* src = p.ws_acc + ((slot0 + k0) * p.gs + n) * kHeadSize + 4 * lane;
+    const long long stride = (long long)p.gs * kHeadSize;
+#pragma unroll 8
+    for (int k = 0; k < cnt; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(src + k * stride);
+      const float w = wts[warp][k];
+      acc.x = fmaf(w, a.x, acc.x);
+      acc.y = fmaf(w, a.y, acc.y);
+      acc.z = fmaf(w, a.z, acc.z);
+      acc.w = fmaf(w, a.w, acc.w);
     }
-    lsum = warp_sum(lsum);
-    float acc = 0.f;
-#pragma unroll 4
-    for (int k = 0; k < nparts; ++k) {
-      const long long r = (slot0 + k) * p.gs + n;
-      acc += p.ws_acc[r * kHeadSize + tid] * __expf(p.ws_ml[r * 2] - M);
-    }
-    out[info.ooff[n] + tid] = from_float<T>(acc / lsum);
+    __syncwarp();
+  }
+  T* dst = static_cast<T*>(p.out) + info->ooff[n] + 4 * lane;
+  const T o0 = from_float<T>(acc.x), o1 = from_float<T>(acc.y), o2 = from_float<T>(acc.z), o3 = from_float<T>(acc.w);
+  if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+    uint2 w;
+    w.x = (uint32_t)(*reinterpret_cast<const unsigned short*>(&o0)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&o1)) << 16);
+    w.y = (uint32_t)(*reinterpret_cast<const unsigned short*>(&o2)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&o3)) << 16);
+    *reinterpret_cast<uint2*>(dst) = w;
+  } else {
+    dst[0] = o0;
+    dst[1] = o1;
+    dst[2] = o2;
+    dst[3] = o3;
   }
 }
 
@@ -494,6 +527,7 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
   cfg.stream = stream;
   cfg.attrs = pdl;
   cfg.numAttrs = 1;
+  prm.num_items = items;
   if ((e = cudaLaunchKernelEx(&cfg, kern, prm)) != cudaSuccess) return record_cuda_error(e);
   if (pl.max_parts > 1) {
     static bool carve[kMaxDevicesTracked] = {};
@@ -502,8 +536,9 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
                            cudaSharedmemCarveoutMaxShared);
       carve[dev] = true;
     }
-    cfg.gridDim = dim3((unsigned)items, (unsigned)pl.head_tiles);
-    cfg.blockDim = dim3(kHeadSize);
+    const long long units = items * pl.head_tiles * pl.gs;
+    cfg.gridDim = dim3((unsigned)((units + kMergeWarps - 1) / kMergeWarps));
+    cfg.blockDim = dim3(kMergeWarps * 32);
     cfg.dynamicSmemBytes = 0;
     if ((e = cudaLaunchKernelEx(&cfg, paged_attn_merge_kernel<T, BS, MIXED>, prm)) != cudaSuccess)
       return record_cuda_error(e);
