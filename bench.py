@@ -93,6 +93,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel leg at N > 1")
+    ap.add_argument("--no-units", action="store_true",
+                    help="c3: launch one CTA per (item, partition index) instead of the host's work list")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     return ap.parse_args()
 
@@ -641,6 +643,8 @@ def run_native_c3(args):
         attn_bytes.append(a)
         cw_bytes.append(w)
 
+    unit_psize = psize or 512     # the work lists are built for an explicit partition size (512 = library default)
+
     def step(events=None):
         for l in range(L_max):
             n_items, n_rows = plan.active(l)
@@ -657,8 +661,8 @@ def run_native_c3(args):
             ops.paged_attention_mixed(out[:n_rows], packed_q[l % 4][:n_rows], kc, vc, plan.block_tables[l, :n_items],
                                       plan.item_context_len[:n_items], plan.item_q_row[:n_items],
                                       plan.item_group[:n_items], plan.item_scale[:n_items], BLOCK,
-                                      plan.max_context_len, plan.max_group, partition_size=psize, num_stages=nst,
-                                      **new_kv)
+                                      plan.max_context_len, plan.max_group, partition_size=unit_psize, num_stages=nst,
+                                      units=None if args.no_units else plan.units(l, unit_psize), **new_kv)
             if events is not None:
                 events[l][1].record()
 

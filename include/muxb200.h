@@ -203,7 +203,14 @@ typedef struct {
   int32_t partition_size;
   int32_t num_stages;
   int32_t flags;
-  int32_t reserved;
+  int32_t num_units;             /* 0, or the length of `units` */
+  /* Optional work list.  Without it the launch has one CTA per (item, partition index up to the longest item's
+   * count) and the CTAs past an item's last partition leave at once; with context lengths as skewed as a
+   * multiplexed batch's most CTAs are of that kind.  The host knows the lengths, so it may list the real
+   * (item, partition) pairs instead: units[u] = item | partition << 24, every partition of every item with
+   * item_context_len > 0 exactly once, in the order they should start (longest first).  partition_size must
+   * then be given explicitly (the list depends on it); num_items < 2^24. */
+  const int32_t* units;          /* device, [num_units] */
 } mux_attn_mixed_args_t;
 
 size_t mux_paged_attention_mixed_workspace_size(const mux_attn_mixed_args_t* args);

@@ -21,7 +21,7 @@ MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 MUX_DEV_INTERNAL = 32
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 
 class CacheWriteArgs(C.Structure):
@@ -71,7 +71,7 @@ class AttnMixedArgs(C.Structure):
         ("num_items", C.c_int32), ("max_group", C.c_int32),
         ("head_size", C.c_int32), ("block_size", C.c_int32), ("max_context_len", C.c_int32),
         ("dtype", C.c_int32), ("partition_size", C.c_int32), ("num_stages", C.c_int32),
-        ("flags", C.c_int32), ("reserved", C.c_int32),
+        ("flags", C.c_int32), ("num_units", C.c_int32), ("units", C.c_void_p),
     ]
 
 

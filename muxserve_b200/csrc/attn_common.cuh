@@ -52,6 +52,7 @@ struct AttnParams {
   const void* rope_cache;                // fused decode step only: [max_position][64 cos | 64 sin], or nullptr
   long long rope_max_position;
   long long num_items;                   // (sequence, kv head) items of the launch
+  const int* units;                      // mixed launch: optional list of item | partition << 24, one CTA each
 };
 
 // Shared-memory carve-up, identical on host (sizing) and device.

@@ -42,7 +42,17 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
 
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int item = blockIdx.x, part = blockIdx.y, htile = blockIdx.z;
+  int item = blockIdx.x, part = blockIdx.y;
+  const int htile = blockIdx.z;
+  if (MIXED && p.units != nullptr) {  // the host listed the real (item, partition) pairs
+    const int u = p.units[blockIdx.x];
+    item = u & 0xffffff;
+    part = (int)((unsigned)u >> 24);
+    if (item >= p.num_items) {  // a list that does not belong to this launch: nothing is read through it
+      if (threadIdx.x == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
+      return;
+    }
+  }
   const int P = p.pb * BS;
 
   griddep_wait();               // inputs may be written by the previous kernel of the stream
@@ -508,7 +518,7 @@ static int ensure_smem(K kern, int smem, int dev, int* granted) {
 }
 
 template <typename T, int BS, bool MIXED, bool FUSE>
-static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream) {
+static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream, int num_units) {
   int dev = 0;
   DeviceInfo di;
   int st = device_info(&dev, &di);
@@ -521,7 +531,8 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
   pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   pdl[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
+  cfg.gridDim = prm.units != nullptr ? dim3((unsigned)num_units, 1u, (unsigned)pl.head_tiles)
+                                     : dim3((unsigned)items, (unsigned)pl.max_parts, (unsigned)pl.head_tiles);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = (size_t)pl.smem;
   cfg.stream = stream;
@@ -548,11 +559,11 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
 
 template <bool MIXED>
 static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, int block_size,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int num_units = 0) {
   const bool fuse = prm.k_new != nullptr;
 #define MUX_CASE(T, BS)                                                        \
-  return fuse ? launch_typed<T, BS, MIXED, true>(prm, pl, items, stream)       \
-              : launch_typed<T, BS, MIXED, false>(prm, pl, items, stream)
+  return fuse ? launch_typed<T, BS, MIXED, true>(prm, pl, items, stream, num_units) \
+              : launch_typed<T, BS, MIXED, false>(prm, pl, items, stream, num_units)
   if (dtype == MUX_DTYPE_F16) {
     if (block_size == 8) MUX_CASE(__half, 8);
     if (block_size == 16) MUX_CASE(__half, 16);
@@ -794,8 +805,14 @@ static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* 
   prm.rope_cache = rows.rope_cache;
   prm.rope_max_position = rows.rope_max_position;
   mux::bind_workspace(prm, pl, workspace);
+  if (a->num_units < 0) return MUX_ERR_BAD_SHAPE;
+  if (a->num_units > 0) {
+    if (a->units == nullptr) return MUX_ERR_NULL_POINTER;
+    if (a->partition_size <= 0 || a->num_items >= (1 << 24) || pl.max_parts > 128) return MUX_ERR_BAD_SHAPE;
+    prm.units = a->units;
+  }
   return mux::launch<true>(prm, pl, a->num_items, a->dtype, a->block_size,
-                           static_cast<cudaStream_t>(cuda_stream));
+                           static_cast<cudaStream_t>(cuda_stream), a->num_units);
 }
 
 }  // namespace mux

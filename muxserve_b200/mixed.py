@@ -56,6 +56,27 @@ class MixedPlan:
         k = sum(1 for n in self.layers if n > layer)
         return self.item_offset[k], self.row_offset[k]
 
+    def units(self, layer: int, partition_size: int = 512) -> torch.Tensor:
+        """Work list of `layer` for ``ops.paged_attention_mixed(..., units=, partition_size=)``: one int32
+        ``item | partition << 24`` per real (item, partition) pair, full partitions first, so that the launch has
+        no CTA that only finds out it has nothing to do and the longest pieces of work start first."""
+        n_items, _ = self.active(layer)
+        key = (n_items, partition_size)
+        cache = self.__dict__.setdefault("_units", {})
+        if key not in cache:
+            ctx = self.item_context_len[:n_items].cpu().numpy().astype(np.int64)
+            nparts = (ctx + partition_size - 1) // partition_size
+            if n_items >= 1 << 24 or (nparts.size and int(nparts.max()) > 128):
+                raise ValueError("too many items or partitions for a packed work list")
+            item = np.repeat(np.arange(n_items, dtype=np.int64), nparts)
+            first = np.cumsum(nparts) - nparts
+            part = np.arange(item.size, dtype=np.int64) - np.repeat(first, nparts)
+            tokens = np.minimum(partition_size, ctx[item] - part * partition_size)
+            order = np.argsort(-tokens, kind="stable")
+            packed = (item[order] | (part[order] << 24)).astype(np.uint32).view(np.int32)
+            cache[key] = torch.from_numpy(packed.copy()).to(self.item_context_len.device)
+        return cache[key]
+
 
 def build_mixed_plan(batches: Sequence[ModelBatch], device) -> MixedPlan:
     order = sorted(range(len(batches)), key=lambda i: -batches[i].num_layers)

@@ -285,7 +285,8 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                           item_group: torch.Tensor, item_scale: torch.Tensor, block_size: int,
                           max_context_len: int, max_group: int, *, partition_size: int = 0,
                           num_stages: int = 0, flags: int = 0, new_k: Optional[torch.Tensor] = None,
-                          new_v: Optional[torch.Tensor] = None, cos_sin_cache: Optional[torch.Tensor] = None) -> None:
+                          new_v: Optional[torch.Tensor] = None, cos_sin_cache: Optional[torch.Tensor] = None,
+                          units: Optional[torch.Tensor] = None) -> None:
     """One launch for the decode batches of several models sharing the pool.
 
     Item ``i`` is one (sequence, kv head) of some model: q rows
@@ -295,6 +296,8 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
     arrays from per-model batches.  With ``new_k`` / ``new_v`` ([items, 128], one new row per
     item) the call is the whole decode step: every row is first appended at position
     ``item_context_len[i] - 1`` of its block list, as ``decode_attention`` does.
+    ``units`` (``MixedPlan.units(layer, partition_size)``, int32) lists the real (item, partition) pairs so that no
+    CTA is launched for a partition an item does not have; ``partition_size`` must then be the one the list was built for.
     """
     _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, block_tables=block_tables,
                   item_context_len=item_context_len, item_q_row=item_q_row, item_group=item_group,
@@ -323,7 +326,12 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
         item_group=item_group.data_ptr(), item_scale=item_scale.data_ptr(),
         num_items=n, max_group=max_group, head_size=HEAD_SIZE, block_size=block_size,
         max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages, flags=flags)
+        partition_size=partition_size, num_stages=num_stages, flags=flags, num_units=0, units=None)
+    if units is not None:
+        _require_cuda(units=units)
+        if units.dtype != torch.int32 or units.dim() != 1 or not units.is_contiguous() or partition_size <= 0:
+            raise ValueError("units must be a contiguous int32 vector and needs an explicit partition_size")
+        args.num_units, args.units = units.shape[0], units.data_ptr()
     L = lib()
     need = L.mux_paged_attention_mixed_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
