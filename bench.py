@@ -94,7 +94,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel leg at N > 1")
     ap.add_argument("--no-units", action="store_true",
-                    help="c3: launch one CTA per (item, partition index) instead of the host's work list")
+                    help="launch one CTA per (item, partition index) instead of the host's work list")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     return ap.parse_args()
 
@@ -305,6 +305,18 @@ def run_native(args):
     cw_bytes = workloads.cache_write_bytes(S * NT, H)
     out = torch.empty((S, Hq, 128), dtype=dt, device=dev)
     psize, nst = args.partition_size, args.num_stages
+    # Work list from the context lengths the host scheduler holds (it uploads them every step): the real
+    # (sequence, kv head, partition) triples, fullest first, padded to a fixed length for the captured graph.
+    units = units_host = None
+    if not args.no_units:
+        psize = psize or 512
+        import numpy as np
+        real = ops.work_units(ctx_list, psize, num_kv_heads=H)
+        cap = (real.size + 127) // 128 * 128
+        units_np = np.full((cap,), -1, dtype=np.int32)
+        units_np[:real.size] = real
+        units_host = torch.from_numpy(units_np).pin_memory()
+        units = units_host.to(dev)
 
     fused = NT == 1 and not args.two_op
 
@@ -315,13 +327,13 @@ def run_native(args):
                 ev[0].record()
             ops.decode_attention(out, case.q[r], case.k[r], case.v[r], kc, vc, None, case.scale, case.block_tables[r],
                                  case.context_lens, BLOCK, case.max_context_len, partition_size=psize,
-                                 num_stages=nst)
+                                 num_stages=nst, units=units)
         else:
             ops.reshape_and_cache(case.k[r], case.v[r], kc, vc, case.slot_mapping[:, r, :])
             if ev is not None:
                 ev[0].record()
             ops.paged_attention(out, case.q[r], kc, vc, None, case.scale, case.block_tables[r], case.context_lens,
-                                BLOCK, case.max_context_len, partition_size=psize, num_stages=nst)
+                                BLOCK, case.max_context_len, partition_size=psize, num_stages=nst, units=units)
         if ev is not None:
             ev[1].record()
 
@@ -438,7 +450,8 @@ def run_native(args):
     e2e = None
     if not args.no_e2e:
         hs = HostDecodeStep(workloads.ModelShape(args.workload, L, Hq, H, S), BLOCK, dt, kc, vc,
-                            case.block_tables.shape[-1], new_tokens=NT, partition_size=psize, num_stages=nst)
+                            case.block_tables.shape[-1], new_tokens=NT, partition_size=psize, num_stages=nst,
+                            units_capacity=0 if units_host is None else units_host.numel())
         rep = [l % L_res for l in range(L)]
         pin = lambda t: t.cpu().pin_memory()
         qh, kh, vh = pin(case.q[rep]), pin(case.k[rep]), pin(case.v[rep])
@@ -446,7 +459,7 @@ def run_native(args):
         smh = pin(case.slot_mapping[:, rep, :].contiguous())
         ch = pin(case.context_lens)
         oh = torch.empty((L, S, Hq, 128), dtype=dt).pin_memory()
-        run_e2e = lambda: hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len)
+        run_e2e = lambda: hs.run(qh, kh, vh, bth, smh, ch, oh, case.max_context_len, units_host=units_host)
         for _ in range(3):
             run_e2e()
         e2e_mode = "eager"
@@ -568,6 +581,8 @@ def run_native(args):
                        "placement": ("1 model on 1 GPU" if world == 1 else
                                      f"{world} independent model replicas, one per GPU, no data-path collective"),
                        "partition_size": psize or "library default", "num_stages": nst or "library default",
+                       "work_list": "none" if units is None else
+                       f"{int((units >= 0).sum())} (sequence, kv head, partition) units from the host's context lengths",
                        "launch": "CUDA graph replay of one step" if graph is not None else "eager (Python call per op)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic,

@@ -142,7 +142,14 @@ typedef struct {
   int32_t partition_size;      /* tokens, multiple of block_size; 0 = library heuristic */
   int32_t num_stages;          /* depth of the shared-memory block ring (multiple of 4, <= 16); 0 = default */
   int32_t flags;               /* reserved, must be 0 */
-  int32_t reserved;
+  int32_t num_units;           /* 0, or the length of `units` */
+  /* Optional work list (see mux_attn_mixed_args_t.units): units[u] = item | partition << 24 with
+   * item = sequence * num_kv_heads + kv head, every partition of every sequence with context_lens > 0 exactly
+   * once, fullest first.  For a host that knows the context lengths it uploads (the reference's scheduler does,
+   * csrc/batch_scheduler.cpp:135-140): the launch then has no CTA for a partition a sequence does not have.
+   * partition_size must be given explicitly; num_seqs * num_kv_heads < 2^24.  Negative entries are padding
+   * (a list kept at a fixed length for a captured CUDA graph): their CTAs leave at once. */
+  const int32_t* units;        /* device, [num_units] */
 } mux_attn_args_t;
 
 size_t mux_paged_attention_workspace_size(const mux_attn_args_t* args);

@@ -21,7 +21,7 @@ MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 MUX_DEV_INTERNAL = 32
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 
 class CacheWriteArgs(C.Structure):
@@ -55,7 +55,7 @@ class AttnArgs(C.Structure):
         ("num_seqs", C.c_int32), ("num_q_heads", C.c_int32), ("num_kv_heads", C.c_int32),
         ("head_size", C.c_int32), ("block_size", C.c_int32), ("max_context_len", C.c_int32),
         ("dtype", C.c_int32), ("partition_size", C.c_int32), ("num_stages", C.c_int32),
-        ("flags", C.c_int32), ("reserved", C.c_int32),
+        ("flags", C.c_int32), ("num_units", C.c_int32), ("units", C.c_void_p),
     ]
 
 

@@ -44,8 +44,9 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int item = blockIdx.x, part = blockIdx.y;
   const int htile = blockIdx.z;
-  if (MIXED && p.units != nullptr) {  // the host listed the real (item, partition) pairs
+  if (p.units != nullptr) {  // the host listed the real (item, partition) pairs
     const int u = p.units[blockIdx.x];
+    if (u < 0) return;  // padding of a list kept at a fixed length (launch dimensions frozen in a CUDA graph)
     item = u & 0xffffff;
     part = (int)((unsigned)u >> 24);
     if (item >= p.num_items) {  // a list that does not belong to this launch: nothing is read through it
@@ -727,8 +728,14 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.rope_cache = rows.rope_cache;
   prm.rope_max_position = rows.rope_max_position;
   mux::bind_workspace(prm, pl, workspace);
+  if (a->num_units < 0) return MUX_ERR_BAD_SHAPE;
+  if (a->num_units > 0) {
+    if (a->units == nullptr) return MUX_ERR_NULL_POINTER;
+    if (a->partition_size <= 0 || items >= (1 << 24) || pl.max_parts > 128) return MUX_ERR_BAD_SHAPE;
+    prm.units = a->units;
+  }
   return mux::launch<false>(prm, pl, items, a->dtype, a->block_size,
-                            static_cast<cudaStream_t>(cuda_stream));
+                            static_cast<cudaStream_t>(cuda_stream), a->num_units);
 }
 
 }  // namespace mux

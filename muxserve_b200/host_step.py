@@ -22,7 +22,7 @@ from .workloads import HEAD_SIZE, ModelShape
 class HostDecodeStep:
     def __init__(self, shape: ModelShape, block_size: int, dtype: torch.dtype, key_cache: torch.Tensor,
                  value_cache: torch.Tensor, max_blocks_per_seq: int, new_tokens: int = 1, depth: int = 4,
-                 partition_size: int = 0, num_stages: int = 0, fused: bool = True):
+                 partition_size: int = 0, num_stages: int = 0, fused: bool = True, units_capacity: int = 0):
         dev = key_cache.device
         self.shape, self.block_size, self.dtype = shape, block_size, dtype
         self.kc, self.vc = key_cache, value_cache
@@ -37,6 +37,8 @@ class HostDecodeStep:
         self.bt = torch.empty((depth, S, shape.num_kv_heads, max_blocks_per_seq), dtype=torch.int32, device=dev)
         self.slots = torch.empty((T, shape.num_layers, shape.num_kv_heads), dtype=torch.int64, device=dev)
         self.ctx = torch.empty((S,), dtype=torch.int32, device=dev)
+        # optional work list (ops.work_units of the host's context lengths, padded with -1 to a fixed length)
+        self.units = torch.empty((units_capacity,), dtype=torch.int32, device=dev) if units_capacity > 0 else None
         self.copy_stream = torch.cuda.Stream(device=dev)
         self.out_stream = torch.cuda.Stream(device=dev)
         self.ready = [torch.cuda.Event() for _ in range(depth)]
@@ -48,7 +50,7 @@ class HostDecodeStep:
 
     def run(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, block_tables_host: torch.Tensor,
             slot_mapping_host: torch.Tensor, context_lens_host: torch.Tensor, out_host: torch.Tensor,
-            max_context_len: int) -> None:
+            max_context_len: int, units_host: torch.Tensor = None) -> None:
         """All ``*_host`` tensors are pinned CPU tensors: q/out [L, S, Hq, D], k/v [L, T, H, D],
         block_tables [L, S, H, max_blocks] int32, slot_mapping [T, L, H] int64, context_lens [S] int32.
         Returns when everything is enqueued; the caller's stream is ordered after the last download."""
@@ -61,6 +63,9 @@ class HostDecodeStep:
             self.ctx.copy_(context_lens_host, non_blocking=True)
             self.slots.copy_(slot_mapping_host, non_blocking=True)
             h2d += self.ctx.numel() * 4 + self.slots.numel() * 8
+            if units_host is not None:
+                self.units.copy_(units_host, non_blocking=True)
+                h2d += self.units.numel() * 4
         for l in range(L):
             b = l % self.depth
             if l >= self.depth:
@@ -76,7 +81,8 @@ class HostDecodeStep:
             if self.fused:
                 ops.decode_attention(self.out[b], self.q[b], self.k[b], self.v[b], self.kc, self.vc, None,
                                      HEAD_SIZE ** -0.5, self.bt[b], self.ctx, self.block_size, max_context_len,
-                                     partition_size=self.partition_size, num_stages=self.num_stages)
+                                     partition_size=self.partition_size, num_stages=self.num_stages,
+                                     units=self.units if units_host is not None else None)
             else:
                 ops.reshape_and_cache(self.k[b], self.v[b], self.kc, self.vc, self.slots[:, l, :])
                 ops.paged_attention(self.out[b], self.q[b], self.kc, self.vc, None, HEAD_SIZE ** -0.5, self.bt[b],

@@ -64,17 +64,9 @@ class MixedPlan:
         key = (n_items, partition_size)
         cache = self.__dict__.setdefault("_units", {})
         if key not in cache:
-            ctx = self.item_context_len[:n_items].cpu().numpy().astype(np.int64)
-            nparts = (ctx + partition_size - 1) // partition_size
-            if n_items >= 1 << 24 or (nparts.size and int(nparts.max()) > 128):
-                raise ValueError("too many items or partitions for a packed work list")
-            item = np.repeat(np.arange(n_items, dtype=np.int64), nparts)
-            first = np.cumsum(nparts) - nparts
-            part = np.arange(item.size, dtype=np.int64) - np.repeat(first, nparts)
-            tokens = np.minimum(partition_size, ctx[item] - part * partition_size)
-            order = np.argsort(-tokens, kind="stable")
-            packed = (item[order] | (part[order] << 24)).astype(np.uint32).view(np.int32)
-            cache[key] = torch.from_numpy(packed.copy()).to(self.item_context_len.device)
+            from .ops import work_units
+            cache[key] = work_units(self.item_context_len[:n_items].cpu().numpy(), partition_size,
+                                    self.item_context_len.device)
         return cache[key]
 
 

@@ -131,7 +131,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                     block_tables: torch.Tensor, context_lens: torch.Tensor, block_size: int,
                     max_context_len: int, *, num_kv_heads: Optional[int] = None,
                     partition_size: int = 0, num_stages: int = 0, flags: int = 0,
-                    seq_rows: Optional[torch.Tensor] = None, _new_kv=None, _rope=None) -> None:
+                    seq_rows: Optional[torch.Tensor] = None, units: Optional[torch.Tensor] = None,
+                    _new_kv=None, _rope=None) -> None:
     """Decode attention of one query token per sequence over the paged pool.
 
     ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
@@ -142,6 +143,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
     ``None`` for contiguous groups.  ``context_lens``: int32 [S], counting the
     token written by this step's ``reshape_and_cache``.  ``seq_rows`` (int32 [S], optional):
     sequence ``s`` uses row ``seq_rows[s]`` of ``block_tables`` (``device_tables.DeviceBlockTables``).
+    ``units`` (``work_units(host context lengths, H, partition_size)``, optional): the real (item, partition) pairs,
+    so that no CTA is launched for a partition a sequence does not have; needs the same explicit ``partition_size``.
     """
     _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, head_mapping=head_mapping,
                   block_tables=block_tables, context_lens=context_lens)
@@ -195,7 +198,12 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
         bt_seq_stride=bt_ss, bt_head_stride=bt_hs, context_lens=context_lens.data_ptr(), seq_rows=sr_ptr,
         scale=float(scale), num_seqs=S, num_q_heads=Hq, num_kv_heads=H, head_size=HEAD_SIZE,
         block_size=block_size, max_context_len=int(max_context_len), dtype=_dtype_code(q, "q"),
-        partition_size=partition_size, num_stages=num_stages, flags=flags)
+        partition_size=partition_size, num_stages=num_stages, flags=flags, num_units=0, units=None)
+    if units is not None:
+        _require_cuda(units=units)
+        if units.dtype != torch.int32 or units.dim() != 1 or not units.is_contiguous() or partition_size <= 0:
+            raise ValueError("units must be a contiguous int32 vector and needs an explicit partition_size")
+        args.num_units, args.units = units.shape[0], units.data_ptr()
     L = lib()
     need = L.mux_paged_attention_workspace_size(C.byref(args))
     ws = _workspace(need, q.device)
@@ -260,6 +268,30 @@ def rotary_embedding(positions: torch.Tensor, q: Optional[torch.Tensor], k: Opti
     check(lib().mux_rotary_embedding(C.byref(args), _stream()), "rotary_embedding")
     global launch_count
     launch_count += 1 if T > 0 and Hq + Hk > 0 else 0
+
+
+def work_units(item_context_lens, partition_size: int, device=None, num_kv_heads: Optional[int] = None):
+    """Work list for the ``units=`` argument of the attention ops, from context lengths the HOST holds.
+
+    ``item_context_lens``: one length per (sequence, kv head) item — or one per sequence together with
+    ``num_kv_heads`` (item = sequence * num_kv_heads + kv head).  Returns int32 ``item | partition << 24`` for every
+    real (item, partition) pair, fullest partitions first (a numpy array, or a tensor on ``device``)."""
+    import numpy as np
+    ctx = np.asarray(item_context_lens, dtype=np.int64).reshape(-1)
+    if num_kv_heads is not None:
+        ctx = np.repeat(ctx, num_kv_heads)
+    if partition_size <= 0:
+        raise ValueError("the work list is built for an explicit partition size")
+    nparts = (np.maximum(ctx, 0) + partition_size - 1) // partition_size
+    if ctx.size >= 1 << 24 or (nparts.size and int(nparts.max()) > 128):
+        raise ValueError("too many items or partitions for a packed work list")
+    item = np.repeat(np.arange(ctx.size, dtype=np.int64), nparts)
+    first = np.cumsum(nparts) - nparts
+    part = np.arange(item.size, dtype=np.int64) - np.repeat(first, nparts)
+    tokens = np.minimum(partition_size, ctx[item] - part * partition_size)
+    order = np.argsort(-tokens, kind="stable")
+    packed = (item[order] | (part[order] << 24)).astype(np.uint32).view(np.int32).copy()
+    return packed if device is None else torch.from_numpy(packed).to(device)
 
 
 def decode_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,

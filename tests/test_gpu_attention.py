@@ -290,3 +290,34 @@ def test_bounded_wait_runs_out_and_is_reported(env, built_lib):
     _, _, ref = gu.oracle_step(case, kc, vc)
     gu.assert_close(out, ref, "after a timed-out wait")
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("Hq,H,psize", [(8, 8, 64), (16, 2, 128), (4, 4, 512)])
+def test_work_list_changes_the_grid_not_the_result(env, Hq, H, psize):
+    """units= (real (item, partition) pairs from host-held context lengths, -1 padded) is bit-identical to the full grid,
+    for the plain op and for the fused decode step."""
+    ops, gu = env
+    import numpy as np
+    ctx = [1, 63, 64, 65, 700, 129, 4, 1000]
+    case, kc, vc = gu.make_case(len(ctx), Hq, H, ctx, 16, torch.float16, seed=55, num_blocks=2048)
+    real = ops.work_units(ctx, psize, num_kv_heads=H)
+    assert real.size == sum((c + psize - 1) // psize for c in ctx) * H
+    padded = np.full((real.size + 37,), -1, dtype=np.int32)
+    padded[:real.size] = real
+    units = torch.from_numpy(padded).cuda()
+    a, b = torch.empty_like(case.q[0]), torch.empty_like(case.q[0])
+    ops.paged_attention(a, case.q[0], kc, vc, None, case.scale, case.block_tables[0], case.context_lens, 16,
+                        case.max_context_len, partition_size=psize)
+    ops.paged_attention(b, case.q[0], kc, vc, None, case.scale, case.block_tables[0], case.context_lens, 16,
+                        case.max_context_len, partition_size=psize, units=units)
+    assert torch.equal(a, b)
+    kc1, vc1, kc2, vc2 = kc.clone(), vc.clone(), kc.clone(), vc.clone()
+    ops.decode_attention(a, case.q[0], case.k[0], case.v[0], kc1, vc1, None, case.scale, case.block_tables[0],
+                         case.context_lens, 16, case.max_context_len, partition_size=psize)
+    ops.decode_attention(b, case.q[0], case.k[0], case.v[0], kc2, vc2, None, case.scale, case.block_tables[0],
+                         case.context_lens, 16, case.max_context_len, partition_size=psize, units=units)
+    assert torch.equal(a, b) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert ops.device_status() == 0
+    with pytest.raises(ValueError):
+        ops.paged_attention(b, case.q[0], kc, vc, None, case.scale, case.block_tables[0], case.context_lens, 16,
+                            case.max_context_len, units=units)        # the list needs its partition size
