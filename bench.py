@@ -309,7 +309,7 @@ def run_native(args):
     # (sequence, kv head, partition) triples, fullest first, padded to a fixed length for the captured graph.
     units = units_host = None
     if not args.no_units:
-        psize = psize or 512
+        psize = psize or ops.suggest_partition_size(S * H, Hq // H, dev)
         import numpy as np
         real = ops.work_units(ctx_list, psize, num_kv_heads=H)
         cap = (real.size + 127) // 128 * 128
