@@ -50,7 +50,7 @@ DTYPES = {"f16": torch.float16, "bf16": torch.bfloat16}
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused decode kernel, from the ncu capture
 # summarised in profiles/paged_attn_kernel_c2_fused_small.md (same per-launch work as a layer of c2, smaller pool).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 1204517000 + 12780544}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 1204193000 + 14504960}
 
 
 _JSON_OUT = None
