@@ -495,6 +495,11 @@ def run_native(args):
     if world > 1 and not args.no_tp and H % world == 0:
         Hl, Hql = H // world, Hq // world
         full = torch.zeros((S, Hq * 128), dtype=dt, device=dev)
+        # the shard's own partition size and work list (fewer items per launch than the whole model has)
+        tp_psize, tp_units = args.partition_size, None
+        if not args.no_units:
+            tp_psize = tp_psize or ops.suggest_partition_size(S * Hl, Hq // H, dev)
+            tp_units = ops.work_units(ctx_list, tp_psize, dev, num_kv_heads=Hl)
 
         def tp_step(allreduce=True, attention=True):
             for l in range(L):
@@ -502,12 +507,12 @@ def run_native(args):
                 if attention and fused:
                     ops.decode_attention(out[:, :Hql], case.q[r][:, :Hql], case.k[r][:, :Hl], case.v[r][:, :Hl], kc, vc,
                                          None, case.scale, case.block_tables[r][:, :Hl], case.context_lens, BLOCK,
-                                         case.max_context_len, partition_size=psize, num_stages=nst)
+                                         case.max_context_len, partition_size=tp_psize, num_stages=nst, units=tp_units)
                 elif attention:
                     ops.reshape_and_cache(case.k[r][:, :Hl], case.v[r][:, :Hl], kc, vc, case.slot_mapping[:, r, :Hl])
                     ops.paged_attention(out[:, :Hql], case.q[r][:, :Hql], kc, vc, None, case.scale,
                                         case.block_tables[r][:, :Hl], case.context_lens, BLOCK, case.max_context_len,
-                                        partition_size=psize, num_stages=nst)
+                                        partition_size=tp_psize, num_stages=nst, units=tp_units)
                 if allreduce:
                     dist.all_reduce(full)
 
