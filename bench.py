@@ -831,11 +831,14 @@ def run_native_prefill(args):
     scale = 128 ** -0.5
     slot_layers = [slots[:, l, :] for l in range(L)]
 
+    # work list from the prompt lengths the host holds (input_metadata.prompt_lens is a host list in the reference)
+    punits = None if args.no_units else ops.prefill_work_units(lens.tolist(), Hq, dev)
+
     def step():          # one launch per layer: prompt attention with the cache write of every token inside
         for l in range(L):
             i = l % Lq
             ops.prefill_attention(out, q[i], k[i], v[i], cu, max_len, scale, key_cache=kc, value_cache=vc,
-                                  slot_mapping=slot_layers[l])
+                                  slot_mapping=slot_layers[l], units=punits)
 
     def step_two_op():   # the reference's two calls per layer
         for l in range(L):
@@ -883,7 +886,7 @@ def run_native_prefill(args):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
             ops.prefill_attention(out, q[i], k[i], v[i], cu, max_len, scale, key_cache=kc, value_cache=vc,
-                                  slot_mapping=slot_layers[l])
+                                  slot_mapping=slot_layers[l], units=punits)
             b.record(stream)
             evs.append((a, b))
         torch.cuda.synchronize()
@@ -899,22 +902,29 @@ def run_native_prefill(args):
     last_h = torch.empty((S, Hq, 128), dtype=dt).pin_memory()
     cu_d, slots_d, tables_d = torch.empty_like(cu), torch.empty_like(slots), torch.empty_like(tables)
 
+    punits_h = None if punits is None else punits.cpu().pin_memory()
+    punits_d = None if punits is None else torch.empty_like(punits)
+
     def e2e_step():      # the reference's hand-over: the [T, L, H] int64 slot mapping goes up every step
+        if punits_h is not None:
+            punits_d.copy_(punits_h, non_blocking=True)
         cu_d.copy_(cu_h, non_blocking=True)
         slots_d.copy_(slots_h, non_blocking=True)
         for l in range(L):
             i = l % Lq
             ops.prefill_attention(out, q[i], k[i], v[i], cu_d, max_len, scale, key_cache=kc, value_cache=vc,
-                                  slot_mapping=slots_d[:, l, :])
+                                  slot_mapping=slots_d[:, l, :], units=punits_d)
         last_h.copy_(out[last_rows], non_blocking=True)
 
     def e2e_step_tables():   # the prompts' block lists [L, S, H, max_blocks] int32 go up instead
+        if punits_h is not None:
+            punits_d.copy_(punits_h, non_blocking=True)
         cu_d.copy_(cu_h, non_blocking=True)
         tables_d.copy_(tables_h, non_blocking=True)
         for l in range(L):
             i = l % Lq
             ops.prefill_attention(out, q[i], k[i], v[i], cu_d, max_len, scale, key_cache=kc, value_cache=vc,
-                                  block_tables=tables_d[l])
+                                  block_tables=tables_d[l], units=punits_d)
         last_h.copy_(out[last_rows], non_blocking=True)
 
     e2e = None

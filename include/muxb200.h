@@ -329,7 +329,13 @@ typedef struct {
   const int32_t* block_tables;   /* device, [num_seqs, num_kv_heads, max_blocks] by the two strides (elements) */
   int64_t bt_seq_stride, bt_head_stride;
   int32_t max_blocks_per_seq;
-  int32_t reserved;
+  int32_t num_units;             /* 0, or the number of (prompt, q head, query tile) triples in `units` */
+  /* Optional work list for a host that knows the prompt lengths (the reference's does: input_metadata.prompt_lens is
+   * a host list): units[2u] = prompt, units[2u + 1] = q head | query tile << 16, one entry per 128-row query tile
+   * of every (prompt, q head), longest prompts first and the tiles of one (prompt, head) together, last tile first.
+   * Without it the grid is (tiles of the longest prompt) x heads x prompts and the CTAs of shorter prompts' missing
+   * tiles leave at once.  Negative prompt = padding. */
+  const int32_t* units;          /* device, [num_units][2] */
 } mux_prefill_args_t;
 
 int mux_prefill_attention(const mux_prefill_args_t* args, void* cuda_stream);

@@ -21,7 +21,7 @@ MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 MUX_DEV_INTERNAL = 32
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 
 class CacheWriteArgs(C.Structure):
@@ -117,7 +117,7 @@ class PrefillArgs(C.Structure):
         ("key_cache", C.c_void_p), ("value_cache", C.c_void_p), ("slot_mapping", C.c_void_p),
         ("slot_token_stride", C.c_int64), ("slot_head_stride", C.c_int64), ("num_blocks", C.c_int64),
         ("block_tables", C.c_void_p), ("bt_seq_stride", C.c_int64), ("bt_head_stride", C.c_int64),
-        ("max_blocks_per_seq", C.c_int32), ("reserved", C.c_int32),
+        ("max_blocks_per_seq", C.c_int32), ("num_units", C.c_int32), ("units", C.c_void_p),
     ]
 
 

@@ -70,6 +70,8 @@ struct Params {
   const int* bt;                            // block lists instead of slots (slots == nullptr)
   long long bt_ss, bt_hs;
   int max_blocks;
+  const int* units;                         // optional work list: (prompt, q head | query tile << 16) per CTA
+  int num_seqs, num_q_heads;
 };
 
 constexpr int smem_bytes() { return kQBytes + 2 * kStages * kStepBytes + 2048; }  // tiles + barriers + 128 slots
@@ -354,8 +356,19 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
                     const __grid_constant__ CUtensorMap tmv, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];  // the swizzle pattern repeats every 1024 bytes
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq = blockIdx.z, head = blockIdx.y;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // the tiles with the most work start first
+  int seq = blockIdx.z, head = blockIdx.y;
+  int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // the tiles with the most work start first
+  if (p.units != nullptr) {  // the host listed the real (prompt, q head, query tile) triples
+    seq = p.units[2 * blockIdx.x];
+    const int hq = p.units[2 * blockIdx.x + 1];
+    head = hq & 0xffff;
+    qt = (int)((unsigned)hq >> 16);
+    if (seq < 0) return;  // padding
+    if (seq >= p.num_seqs || head >= p.num_q_heads) {
+      if (threadIdx.x == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
+      return;
+    }
+  }
 
   if (tid == kKWarp * 32) {  // the copy descriptors do not depend on the previous kernel: fetch them early
     prefetch_tensormap(&tmq);
@@ -743,8 +756,9 @@ static int launch(const mux_prefill_args_t* a, const CUtensorMap& mq, const CUte
   pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   pdl[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)((a->max_prompt_len + kTile - 1) / kTile), (unsigned)a->num_q_heads,
-                     (unsigned)a->num_seqs);
+  cfg.gridDim = a->num_units > 0 ? dim3((unsigned)a->num_units)
+                                 : dim3((unsigned)((a->max_prompt_len + kTile - 1) / kTile), (unsigned)a->num_q_heads,
+                                        (unsigned)a->num_seqs);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -775,6 +789,7 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
     if (a->num_blocks <= 0) return MUX_ERR_BAD_SHAPE;
     if (!aligned16(a->key_cache) || !aligned16(a->value_cache)) return MUX_ERR_MISALIGNED;
   }
+  if (a->num_units < 0 || (a->num_units > 0 && a->units == nullptr)) return a->num_units < 0 ? MUX_ERR_BAD_SHAPE : MUX_ERR_NULL_POINTER;
   unsigned* status = device_status_ptr();
   if (status == nullptr) return MUX_ERR_CUDA;
   EncodeTiledFn enc = nullptr;
@@ -806,6 +821,9 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
   prm.bt_ss = a->bt_seq_stride;
   prm.bt_hs = a->bt_head_stride;
   prm.max_blocks = a->max_blocks_per_seq;
+  prm.units = a->num_units > 0 ? a->units : nullptr;
+  prm.num_seqs = a->num_seqs;
+  prm.num_q_heads = a->num_q_heads;
   if (a->dtype == MUX_DTYPE_F16) return launch<__half, false>(a, mq, mk, mv, prm, stream);
   return launch<__nv_bfloat16, true>(a, mq, mk, mv, prm, stream);
 }

@@ -405,11 +405,32 @@ def cu_seqlens_from_prompt_lens(prompt_lens, device) -> torch.Tensor:
     return torch.tensor(cu, dtype=torch.int32, device=device)
 
 
+def prefill_work_units(prompt_lens, num_q_heads: int, device=None):
+    """Work list for ``prefill_attention(..., units=)`` from the prompt lengths the HOST holds: int32 [U, 2] rows
+    ``(prompt, q head | query tile << 16)``, one per 128-row query tile of every (prompt, q head); prompts in order
+    of decreasing length, the tiles of one (prompt, head) together (they share their K/V in L2), last tile first."""
+    import numpy as np
+    lens = np.asarray(prompt_lens, dtype=np.int64).reshape(-1)
+    if num_q_heads >= 1 << 16 or (lens.size and (int(lens.max()) + 127) // 128 >= 1 << 15):
+        raise ValueError("too many heads or tiles for a packed work list")
+    rows = []
+    for s in np.argsort(-lens, kind="stable"):
+        tiles = (int(lens[s]) + 127) // 128
+        if tiles == 0:
+            continue
+        qt = np.arange(tiles - 1, -1, -1, dtype=np.int64)
+        h = np.arange(num_q_heads, dtype=np.int64)
+        hq = (h[:, None] | (qt[None, :] << 16)).reshape(-1)
+        rows.append(np.stack([np.full(hq.size, s, dtype=np.int64), hq], axis=1))
+    packed = (np.concatenate(rows) if rows else np.zeros((0, 2), dtype=np.int64)).astype(np.int32)
+    return packed if device is None else torch.from_numpy(packed).to(device)
+
+
 def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                       cu_seqlens: torch.Tensor, max_prompt_len: int, scale: float,
                       key_cache: Optional[torch.Tensor] = None, value_cache: Optional[torch.Tensor] = None,
                       slot_mapping: Optional[torch.Tensor] = None,
-                      block_tables: Optional[torch.Tensor] = None) -> None:
+                      block_tables: Optional[torch.Tensor] = None, units: Optional[torch.Tensor] = None) -> None:
     """Causal self-attention of every prompt over its own tokens (the prompt branch of PagedAttentionWithRoPE).
 
     ``q``/``out`` [T, Hq(*128)], ``k``/``v`` [T, H(*128)] hold the rows of all prompts back to back;
@@ -417,7 +438,9 @@ def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: to
     With ``key_cache``/``value_cache``/``slot_mapping`` (int64 [T, H], e.g. ``slot_mapping[:, layer, :]``) the same
     launch also writes every K/V row to its pool slot, bit for bit what ``reshape_and_cache`` would write.
     ``block_tables`` (int32 [S, H, max_blocks], this layer's lists as the decode ops take them) may stand in for
-    ``slot_mapping``: token t of a prompt goes to offset ``t % block_size`` of block ``t // block_size`` of its list."""
+    ``slot_mapping``: token t of a prompt goes to offset ``t % block_size`` of block ``t // block_size`` of its list.
+    ``units`` (``prefill_work_units(prompt_lens, Hq, device)``, int32 [U, 2]): the real (prompt, q head, query tile)
+    triples, longest prompts first, so that no CTA is launched for a tile a prompt does not have."""
     _require_cuda(out=out, q=q, k=k, v=v, cu_seqlens=cu_seqlens, key_cache=key_cache, value_cache=value_cache,
                   slot_mapping=slot_mapping, block_tables=block_tables)
     if cu_seqlens.dtype != torch.int32 or cu_seqlens.dim() != 1 or not cu_seqlens.is_contiguous():
@@ -436,7 +459,7 @@ def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: to
         raise ValueError("cu_seqlens needs at least one entry")
     pool = dict(block_size=0, key_cache=None, value_cache=None, slot_mapping=None, slot_token_stride=0,
                 slot_head_stride=0, num_blocks=0, block_tables=None, bt_seq_stride=0, bt_head_stride=0,
-                max_blocks_per_seq=0, reserved=0)
+                max_blocks_per_seq=0, num_units=0, units=None)
     if key_cache is not None or value_cache is not None or slot_mapping is not None or block_tables is not None:
         if key_cache is None or value_cache is None or (slot_mapping is None) == (block_tables is None):
             raise ValueError("the cache write needs key_cache, value_cache and ONE of slot_mapping / block_tables")
@@ -461,6 +484,11 @@ def prefill_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: to
                             cu_seqlens=cu_seqlens.data_ptr(), scale=float(scale), num_seqs=S, total_tokens=T,
                             max_prompt_len=int(max_prompt_len), num_q_heads=Hq, num_kv_heads=Hk,
                             head_size=HEAD_SIZE, dtype=code, **pool)
+    if units is not None:
+        _require_cuda(units=units)
+        if units.dtype != torch.int32 or units.dim() != 2 or units.shape[1] != 2 or not units.is_contiguous():
+            raise ValueError("units must be a contiguous int32 [U, 2] tensor")
+        args.num_units, args.units = units.shape[0], units.data_ptr()
     check(lib().mux_prefill_attention(C.byref(args), _stream()), "prefill_attention")
     global launch_count
     launch_count += 1 if S > 0 and T > 0 and max_prompt_len > 0 else 0

@@ -228,3 +228,37 @@ def test_prefill_fuzz(seed):
         reshape_and_cache_ref(k.cpu(), v.cpu(), kc_c, vc_c, slots[:, 1, :].cpu())
         assert torch.equal(kc.cpu().view(torch.int16), kc_c.view(torch.int16))
         assert torch.equal(vc.cpu().view(torch.int16), vc_c.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_prefill_work_list_is_bit_identical(dtype):
+    """units= removes the CTAs of tiles a prompt does not have and reorders the rest; results and pool writes are the same."""
+    import numpy as np
+    from muxserve_b200 import flexstore, ops, workloads
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(77)
+    lens = [300, 5, 0, 1025, 128, 64, 700]
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    T, Hq, H, B, nblk = int(lens_t.sum()), 4, 2, 16, 1024
+    q = torch.randn((T, Hq, 128), generator=gen).to(dtype).to(dev)
+    k = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    v = torch.randn((T, H, 128), generator=gen).to(dtype).to(dev)
+    cu = ops.cu_seqlens_from_prompt_lens(lens, dev)
+    tables, _ = workloads.scatter_block_tables(lens_t, 1, H, B, torch.randperm(nblk, generator=gen).to(dev))
+    real = ops.prefill_work_units(lens, Hq)
+    assert real.shape == (sum((n + 127) // 128 for n in lens) * Hq, 2)
+    padded = np.concatenate([real, np.full((5, 2), -1, dtype=np.int32)])
+    units = torch.from_numpy(padded).to(dev)
+    outs, pools = [], []
+    for u in (None, units):
+        kc, vc = flexstore.allocate_gpu_cache(nblk, B, dtype, dev)
+        workloads.fill_pool_(kc, vc, 5)
+        out = torch.zeros_like(q)
+        ops.prefill_attention(out, q, k, v, cu, max(lens), 128 ** -0.5, key_cache=kc, value_cache=vc,
+                              block_tables=tables[0], units=u)
+        outs.append(out)
+        pools.append((kc, vc))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(pools[0][0], pools[1][0]) and torch.equal(pools[0][1], pools[1][1])
