@@ -663,7 +663,8 @@ def run_native_c3(args):
         attn_bytes.append(a)
         cw_bytes.append(w)
 
-    unit_psize = psize or 512     # the work lists are built for an explicit partition size (512 = library default)
+    # the work lists are built for an explicit partition size
+    unit_psize = psize or (512 if args.no_units else ops.suggest_partition_size(plan.active(0)[0], plan.max_group, dev))
 
     def step(events=None):
         for l in range(L_max):
