@@ -663,8 +663,7 @@ def run_native_c3(args):
         attn_bytes.append(a)
         cw_bytes.append(w)
 
-    # the work lists are built for an explicit partition size
-    unit_psize = psize or (512 if args.no_units else ops.suggest_partition_size(plan.active(0)[0], plan.max_group, dev))
+    unit_psize = psize or 512     # the work lists are built for an explicit partition size (512 = library default)
 
     def step(events=None):
         for l in range(L_max):

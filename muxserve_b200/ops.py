@@ -298,12 +298,10 @@ def suggest_partition_size(num_items: int, group: int, device=None) -> int:
     """Partition size to build a work list for.  With the list's fullest-first order long partitions no longer
     leave a tail, so launches with plenty of items (at least two per resident CTA place) and at most two q heads
     per kv head do best with few or no splits (2048 tokens: no partial results, no merge kernel for contexts up to
-    2048); grouped heads keep 512 (their logits rows take shared memory in proportion to the partition); launches
-    with fewer items than CTA places split finer (256) to fill the GPU."""
+    2048); grouped heads keep 512 (their logits rows take shared memory in proportion to the partition), and so do
+    small launches, which need the split to fill the GPU."""
     sms = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
-    if group <= 2 and num_items >= 2 * 6 * sms:
-        return 2048
-    return 256 if group <= 2 and num_items < 6 * sms else 512   # less than one CTA per place: split finer
+    return 2048 if group <= 2 and num_items >= 2 * 6 * sms else 512
 
 
 def decode_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
