@@ -50,3 +50,39 @@ def test_device_tables_bookkeeping():
         raise AssertionError("expected the table to be full")
     except RuntimeError:
         pass
+
+
+def test_work_units_cover_every_partition_once_fullest_first():
+    import numpy as np
+    from muxserve_b200 import ops
+    ctx = [1, 512, 513, 0, 2048, 77]
+    H, P = 3, 512
+    u = ops.work_units(ctx, P, num_kv_heads=H)
+    item, part = u & 0xffffff, (u.view(np.uint32) >> 24).astype(np.int64)
+    want = {(s * H + h, p) for s, c in enumerate(ctx) for h in range(H) for p in range((c + P - 1) // P)}
+    assert len(u) == len(want) and set(zip(item.tolist(), part.tolist())) == want
+    per_item = np.repeat(np.asarray(ctx), H)
+    tokens = np.minimum(P, per_item[item] - part * P)
+    assert (np.diff(tokens) <= 0).all()                      # fullest partitions first
+    assert (u >= 0).all()                                    # negative values are reserved for padding
+    import pytest
+    with pytest.raises(ValueError):
+        ops.work_units(ctx, 0, num_kv_heads=H)
+
+
+def test_prefill_work_units_group_tiles_of_a_prompt_and_start_with_the_longest():
+    from muxserve_b200 import ops
+    lens = [130, 0, 1000, 128]
+    Hq = 3
+    u = ops.prefill_work_units(lens, Hq)
+    assert u.shape == (sum((n + 127) // 128 for n in lens) * Hq, 2)
+    seqs = u[:, 0].tolist()
+    assert seqs[0] == 2 and 1 not in seqs                    # longest prompt first, empty prompt absent
+    firsts = [seqs.index(s) for s in (2, 0, 3)]
+    assert firsts == sorted(firsts)                          # prompts in order of decreasing length
+    triples = {(int(s), int(hq) & 0xffff, int(hq) >> 16) for s, hq in u}
+    want = {(s, h, t) for s, n in enumerate(lens) for h in range(Hq) for t in range((n + 127) // 128)}
+    assert triples == want
+    # within one (prompt, head) the last tile comes first
+    rows = [(int(hq) >> 16) for s, hq in u if s == 2 and (int(hq) & 0xffff) == 0]
+    assert rows == sorted(rows, reverse=True)
