@@ -743,7 +743,11 @@ def run_native_c3(args):
     if rank == 0:
         peak, peak_src = hbm_peak()
         S_total = sum(b.num_seqs for b in batches)
-        achieved = sum(attn_bytes) / (attn_ms * 1e-3) / 1e9
+        # under graph replay with the fused step a layer index is exactly one attention launch (+ its merge kernel):
+        # the launches' time is the timed region (gaps included); the eager pass's per-launch events carry the
+        # Python call overhead of 60 small launches and are reported beside it
+        span_ms = ms_step if (graph is not None and fused) else attn_ms
+        achieved = (sum(attn_bytes) + (sum(cw_bytes) if fused else 0)) / (span_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": world * S_total / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
@@ -757,8 +761,10 @@ def run_native_c3(args):
                                 "one reshape_and_cache per model and layer + one fused attention launch per layer index")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "kernel": "paged_attn_kernel<mixed> (+ merge)",
-                         "algorithmic_bytes_per_step": sum(attn_bytes), "attention_ms_per_step": attn_ms,
-                         "peak_source": peak_src,
+                         "algorithmic_bytes_per_step": sum(attn_bytes), "attention_ms_per_step": span_ms,
+                         "eager_span_ms": attn_ms, "peak_source": peak_src,
+                         "span": ("timed region (graph replay, one attention launch per layer index)"
+                                  if (graph is not None and fused) else "CUDA events around every attention launch"),
                          "whole_path_gbs": (sum(attn_bytes) + sum(cw_bytes)) / (ms_step * 1e-3) / 1e9},
             "cpu_baseline": None, "e2e": None, "gpu_launches": gpu_launches, "clocks": clocks, "device_status": status,
             "eager_ms_per_step": ms_eager,
