@@ -49,6 +49,21 @@ typedef enum { MUX_DTYPE_F16 = 0, MUX_DTYPE_BF16 = 1 } mux_dtype_t;
 #define MUX_DEV_BAD_SLOT 8u       /* a slot outside the pool was met and skipped */
 #define MUX_DEV_BAD_HEAD_MAPPING 16u /* head_mapping does not give every kv head num_q_heads/num_kv_heads q heads */
 #define MUX_DEV_INTERNAL 32u      /* a kernel found a precondition of its own broken (shared-memory alignment) and left */
+#define MUX_DEV_BAD_GROUP 64u     /* an item_group outside [1, max_group] was met; at most max_group heads were computed */
+
+/* Bits of the `flags` field of the attention argument structs.
+ *
+ * MUX_ATTN_EARLY_KV: the kernels of this library are launched with programmatic dependent launch: a launch
+ * may become resident while the kernels just ahead of it in the stream are still draining, and normally
+ * waits for them before it reads anything.  With this bit the caller states that the launch's index data
+ * (block_tables, context lengths, seq_rows, head_mapping, the item arrays, units) and the KV blocks the
+ * block lists name are NOT written by the (up to two) kernels directly ahead of it in the stream; each CTA
+ * then resolves its item and stages its first KV blocks before it waits, and only q, the new K/V rows and
+ * all writes (pool, workspace, out) stay behind the wait.  True for a decode step through
+ * mux_decode_attention(_mixed): the kernel ahead of a layer's attention produced q/k/v, and the previous
+ * layer's attention appended to blocks of its own layer.  NOT true for mux_paged_attention right after
+ * mux_reshape_and_cache of the same layer, nor right after mux_block_table_append: leave the bit clear there. */
+#define MUX_ATTN_EARLY_KV 1
 
 const char* mux_strerror(int status);
 /* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
@@ -127,7 +142,9 @@ typedef struct {
   const int32_t* head_mapping; /* [num_q_heads] device, or NULL for contiguous groups */
   const int32_t* block_tables; /* device */
   int64_t bt_seq_stride;       /* elements */
-  int64_t bt_head_stride;      /* elements; 0 = all kv heads share one list (plain vLLM layout) */
+  int64_t bt_head_stride;      /* elements; 0 = all kv heads read ONE list (and so the same K/V, a pool block holding
+                                  one head): meaningful for num_kv_heads == 1 or read-only probing, and refused by
+                                  mux_decode_attention when num_kv_heads > 1 (its kv heads would append to one slot) */
   const int32_t* context_lens; /* [num_seqs] device */
   const int32_t* seq_rows;     /* NULL, or [num_seqs] device: sequence s uses row seq_rows[s] of block_tables
                                   (a persistent table kept on the device, see mux_block_table_append) */
@@ -141,14 +158,17 @@ typedef struct {
   int32_t dtype;               /* mux_dtype_t */
   int32_t partition_size;      /* tokens, multiple of block_size; 0 = library heuristic */
   int32_t num_stages;          /* depth of the shared-memory block ring (multiple of 4, <= 16); 0 = default */
-  int32_t flags;               /* reserved, must be 0 */
+  int32_t flags;               /* MUX_ATTN_* bits, 0 = none */
   int32_t num_units;           /* 0, or the length of `units` */
   /* Optional work list (see mux_attn_mixed_args_t.units): units[u] = item | partition << 24 with
    * item = sequence * num_kv_heads + kv head, every partition of every sequence with context_lens > 0 exactly
    * once, fullest first.  For a host that knows the context lengths it uploads (the reference's scheduler does,
    * csrc/batch_scheduler.cpp:135-140): the launch then has no CTA for a partition a sequence does not have.
    * partition_size must be given explicitly; num_seqs * num_kv_heads < 2^24.  Negative entries are padding
-   * (a list kept at a fixed length for a captured CUDA graph): their CTAs leave at once. */
+   * (a list kept at a fixed length for a captured CUDA graph): their CTAs leave at once.  A sequence with an empty
+   * context should be listed with its partition 0 (that CTA writes the zero rows); left out, its rows of `out` are
+   * not written.  The list is read BEFORE the launch waits for the kernels ahead of it in the stream: it must be
+   * complete by then (uploaded by a copy, or written by a kernel that is not the one directly ahead). */
   const int32_t* units;        /* device, [num_units] */
 } mux_attn_args_t;
 
@@ -209,7 +229,7 @@ typedef struct {
   int32_t dtype;
   int32_t partition_size;
   int32_t num_stages;
-  int32_t flags;
+  int32_t flags;                 /* MUX_ATTN_* bits, 0 = none */
   int32_t num_units;             /* 0, or the length of `units` */
   /* Optional work list.  Without it the launch has one CTA per (item, partition index up to the longest item's
    * count) and the CTAs past an item's last partition leave at once; with context lengths as skewed as a
@@ -306,7 +326,9 @@ typedef struct {
   const int32_t* cu_seqlens; /* device, [num_seqs + 1], cu_seqlens[0] = 0, non-decreasing */
   float scale;               /* > 0 */
   int32_t num_seqs;
-  int32_t total_tokens;      /* rows of q / k / v / out */
+  int32_t total_tokens;      /* rows of q / k / v / out; normally cu_seqlens[num_seqs].  Rows of v between a prompt's end
+                                and total_tokens share 64-row steps with real rows and must hold finite values
+                                (they are weighted by 0, and 0 * NaN would poison the step) */
   int32_t max_prompt_len;    /* host-known upper bound of every prompt length (sizes the grid) */
   int32_t num_q_heads;
   int32_t num_kv_heads;
@@ -354,12 +376,55 @@ int mux_block_table_append(int32_t* tables, int64_t layer_stride, int64_t row_st
                            const int32_t* upd_row, const int32_t* upd_block, const int32_t* upd_ids,
                            int32_t num_updates, void* cuda_stream);
 
+/* ------------------------------------------------------------------------
+ * Tensor-parallel output all-reduce over NVLink peer memory.
+ *
+ * Replaces the NCCL all-reduce (sum over the TP group) of the row-parallel o_proj output,
+ * muxserve/flexserver/models/llama.py:131-137,162 (the fork's ParallelLinear.row), for the 16-bit
+ * [tokens, hidden] messages of a decode step, which are latency-bound: one kernel per rank, plain peer
+ * stores / loads and epoch flags, every wait bounded (MUX_DEV_WAIT_TIMEOUT when one runs out).
+ * Every rank ends up with the same bits (fp32 sums in rank order).
+ *
+ * Set-up (host): each rank allocates one exchange buffer of mux_tp_allreduce_buffer_size() bytes,
+ * 256-byte aligned and ZEROED, exports it (CUDA IPC), maps the other ranks' buffers, enables peer
+ * access to their devices and synchronises with them once before the first call.  All ranks must make
+ * the same sequence of calls (count, dtype, algo, num_ctas); calls of one communicator are ordered on
+ * one stream per rank.  in == out is allowed.
+ * ---------------------------------------------------------------------- */
+#define MUX_TP_MAX_WORLD 8
+#define MUX_TP_AUTO 0
+#define MUX_TP_ONE_SHOT 1                      /* each rank pushes its message to all, sums locally */
+#define MUX_TP_TWO_SHOT 2                      /* reduce-scatter by peer loads + all-gather by peer stores */
+#define MUX_TP_ONE_SHOT_MAX_BYTES (512 << 10)  /* MUX_TP_AUTO: largest message that goes one-shot */
+typedef struct {
+  int32_t world;                      /* 2 .. MUX_TP_MAX_WORLD */
+  int32_t rank;
+  void* buffers[MUX_TP_MAX_WORLD];    /* exchange buffer of every rank as mapped in THIS process; [rank] is local */
+  int64_t buffer_bytes;               /* size of each */
+} mux_tp_comm_t;
+
+size_t mux_tp_allreduce_buffer_size(int32_t world, size_t max_message_bytes);
+/* cudaDeviceEnablePeerAccess from the current device to peer_device (already enabled = ok). */
+int mux_tp_enable_peer_access(int32_t peer_device);
+/* out = sum over ranks of in; count elements (multiple of 8) of dtype.  num_ctas 0 = heuristic (<= 64).
+ * MUX_ERR_TOO_LARGE when the message does not fit the exchange buffers. */
+int mux_tp_allreduce(const mux_tp_comm_t* comm, const void* in, void* out, int64_t count, int32_t dtype,
+                     int32_t algo, int32_t num_ctas, void* cuda_stream);
+/* The same device code for a whole world on ONE GPU: rank r uses buffers[r], ins[r], outs[r]; all ranks'
+ * CTAs form one cooperative launch (they wait on one another).  For tests of the protocol without
+ * several GPUs; fails with MUX_ERR_CUDA when the grid cannot be resident at once. */
+int mux_tp_allreduce_emulated(int32_t world, void* const* buffers, int64_t buffer_bytes, const void* const* ins,
+                              void* const* outs, int64_t count, int32_t dtype, int32_t algo, int32_t num_ctas,
+                              void* cuda_stream);
+
 /* Self-test of the failure path: launches one warp that waits, with the same bounded wait the
  * kernels use, on a barrier nothing completes.  The wait gives up after a (shortened) poll limit, well under a second, sets MUX_DEV_WAIT_TIMEOUT and the kernel ends normally: the context stays usable. */
 int mux_selftest_wait_timeout(void* cuda_stream);
 
 /* Reads and clears the device status word (MUX_DEV_* bits) of the current
- * device.  Synchronises the given stream. Returns a negative mux_status_t on failure. */
+ * device.  Synchronises the given stream. Returns a negative mux_status_t on failure.
+ * The word is copied and then cleared by two operations on `cuda_stream`: bits that kernels on OTHER
+ * streams set between the two are lost, so read it from the stream the work ran on (or after a device sync). */
 int mux_device_status(void* cuda_stream);
 
 /* ------------------------------------------------------------------------

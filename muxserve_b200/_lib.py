@@ -20,8 +20,13 @@ MUX_DEV_BAD_CONTEXT = 4
 MUX_DEV_BAD_SLOT = 8
 MUX_DEV_BAD_HEAD_MAPPING = 16
 MUX_DEV_INTERNAL = 32
+MUX_DEV_BAD_GROUP = 64
 
-ABI_VERSION = 11
+MUX_ATTN_EARLY_KV = 1
+
+MUX_TP_AUTO, MUX_TP_ONE_SHOT, MUX_TP_TWO_SHOT = 0, 1, 2
+
+ABI_VERSION = 12
 
 
 class CacheWriteArgs(C.Structure):
@@ -121,6 +126,10 @@ class PrefillArgs(C.Structure):
     ]
 
 
+class TpComm(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("buffers", C.c_void_p * 8), ("buffer_bytes", C.c_int64)]
+
+
 _I32P = C.POINTER(C.c_int32)
 _I64P = C.POINTER(C.c_int64)
 
@@ -141,6 +150,13 @@ SIGNATURES = {
     "mux_prefill_attention": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
     "mux_block_table_append": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
+    "mux_tp_allreduce_buffer_size": (C.c_size_t, [C.c_int32, C.c_size_t]),
+    "mux_tp_enable_peer_access": (C.c_int, [C.c_int32]),
+    "mux_tp_allreduce": (C.c_int, [C.POINTER(TpComm), C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                   C.c_int32, C.c_void_p]),
+    "mux_tp_allreduce_emulated": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p), C.c_int64, C.POINTER(C.c_void_p),
+                                            C.POINTER(C.c_void_p), C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                            C.c_void_p]),
     "mux_selftest_wait_timeout": (C.c_int, [C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),
     "mux_kv_storage_create": (C.c_void_p, [C.c_int32]),

@@ -45,6 +45,7 @@ struct AttnParams {
   int max_parts;
   int max_context_len;
   int nst;         // ring depth in tiles
+  int prod_lanes;  // lanes of the producer warp that issue tiles (divides nst)
   // fused cache write (decode step): the new token's K/V rows, one per (sequence, kv head)
   const void* k_new;
   const void* v_new;
@@ -52,8 +53,24 @@ struct AttnParams {
   const void* rope_cache;                // fused decode step only: [max_position][64 cos | 64 sin], or nullptr
   long long rope_max_position;
   long long num_items;                   // (sequence, kv head) items of the launch
-  const int* units;                      // mixed launch: optional list of item | partition << 24, one CTA each
+  const int* units;                      // optional list of item | partition << 24, one CTA each
+  int flags;                             // MUX_ATTN_* bits of the call
+#ifdef MUX_TRACE
+  unsigned long long* trace;             // scratch builds only: clock64 stamps of CTA 0
+#endif
 };
+
+// Scratch builds (-DMUX_TRACE) stamp the phases of CTA 0 with clock64; product builds compile this away.
+#ifdef MUX_TRACE
+#define MUX_TRACE_AT(slot, who)                                                   \
+  do {                                                                            \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == (who)) p.trace[slot] = clock64(); \
+  } while (0)
+#else
+#define MUX_TRACE_AT(slot, who) \
+  do {                          \
+  } while (0)
+#endif
 
 // Shared-memory carve-up, identical on host (sizing) and device.
 struct SmemLayout {
@@ -82,7 +99,7 @@ __host__ __device__ inline SmemLayout smem_layout(int block_size, int pb, int gs
   L.info = off;
   off += 8 * 8 + 8 * 8 + 8 * 2 * 4 + 16;  // qoff, ooff, ml, geff
   L.bars = off;
-  off += 2 * kMaxStages * 8;
+  off += (2 * kMaxStages + 1) * 8;  // full[], empty[], and one barrier for the staged new rows
   L.total = off;
   return L;
 }
@@ -134,14 +151,18 @@ __device__ __forceinline__ void resolve_heads(const AttnParams& p, const ItemDes
       info->qoff[lane] = row * p.q_s1;
       info->ooff[lane] = row * p.o_s1;
     }
-    if (lane == 0) info->geff = max(0, min(8, d.G - htile * 8));
+    if (lane == 0) {
+      // Shared memory holds p.gs head columns: a group read from device data never widens the tile.
+      if (d.G < 1 || d.G > p.gs * p.head_tiles) atomicOr(p.status, MUX_DEV_BAD_GROUP);
+      info->geff = max(0, min(p.gs, d.G - htile * 8));
+    }
   } else if (p.head_mapping == nullptr) {
     if (lane < 8) {
       long long hq = (long long)d.kvh * d.G + htile * 8 + lane;
       info->qoff[lane] = (long long)d.seq * p.q_s0 + hq * p.q_s1;
       info->ooff[lane] = (long long)d.seq * p.o_s0 + hq * p.o_s1;
     }
-    if (lane == 0) info->geff = max(0, min(8, d.G - htile * 8));
+    if (lane == 0) info->geff = max(0, min(p.gs, d.G - htile * 8));
   } else {
     // General head_mapping: ordered compaction of the q heads mapped to this kv head.
     int count = 0;
@@ -158,7 +179,9 @@ __device__ __forceinline__ void resolve_heads(const AttnParams& p, const ItemDes
     }
     if (lane == 0) {
       if (count != d.G) atomicOr(p.status, MUX_DEV_BAD_HEAD_MAPPING);
-      info->geff = max(0, min(8, count - htile * 8));
+      // A kv head given more q heads than the group keeps only the first `group` of them (status bit above):
+      // the tile never grows beyond the p.gs columns that shared memory and the workspace were sized for.
+      info->geff = max(0, min(p.gs, min(count, d.G) - htile * 8));
     }
   }
 }

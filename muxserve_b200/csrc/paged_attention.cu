@@ -22,11 +22,65 @@
 // small kernel merges the partitions (flash-decoding).
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 
 #include "attn_common.cuh"
 
 namespace mux {
+
+constexpr int kMergeWarps = 4;
+constexpr int kMergeChunk = 128;  // partitions whose weights are staged at a time
+
+// One warp merges the partitions of one q head of one (item, head tile): the lanes reduce (max, sum)
+// over the partitions, turn them into one weight per partition (staged in `wts`, kMergeChunk floats of
+// shared memory owned by the warp) and then each lane accumulates four output elements from 16-byte
+// loads, eight partitions in flight.
+template <typename T>
+__device__ __forceinline__ void merge_one(const AttnParams& p, long long slot0, int n, int nparts, long long ooff,
+                                          float* wts, int lane) {
+  float M = -INFINITY;
+  for (int k = lane; k < nparts; k += 32) M = fmaxf(M, __ldcg(p.ws_ml + ((slot0 + k) * p.gs + n) * 2));
+  M = warp_max(M);
+  float lsum = 0.f;
+  for (int k = lane; k < nparts; k += 32) {
+    const long long r = (slot0 + k) * p.gs + n;
+    lsum += __ldcg(p.ws_ml + r * 2 + 1) * __expf(__ldcg(p.ws_ml + r * 2) - M);
+  }
+  lsum = warp_sum(lsum);
+  const float inv = 1.f / lsum;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < nparts; k0 += kMergeChunk) {
+    const int cnt = min(kMergeChunk, nparts - k0);
+    for (int k = lane; k < cnt; k += 32) wts[k] = __expf(__ldcg(p.ws_ml + ((slot0 + k0 + k) * p.gs + n) * 2) - M) * inv;
+    __syncwarp();
+    const float* src = p.ws_acc + ((slot0 + k0) * p.gs + n) * kHeadSize + 4 * lane;
+    const long long stride = (long long)p.gs * kHeadSize;
+#pragma unroll 8
+    for (int k = 0; k < cnt; ++k) {
+      const float4 a = __ldcg(reinterpret_cast<const float4*>(src + k * stride));
+      const float w = wts[k];
+      acc.x = fmaf(w, a.x, acc.x);
+      acc.y = fmaf(w, a.y, acc.y);
+      acc.z = fmaf(w, a.z, acc.z);
+      acc.w = fmaf(w, a.w, acc.w);
+    }
+    __syncwarp();
+  }
+  T* dst = static_cast<T*>(p.out) + ooff + 4 * lane;
+  const T o0 = from_float<T>(acc.x), o1 = from_float<T>(acc.y), o2 = from_float<T>(acc.z), o3 = from_float<T>(acc.w);
+  if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+    uint2 w;
+    w.x = (uint32_t)(*reinterpret_cast<const unsigned short*>(&o0)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&o1)) << 16);
+    w.y = (uint32_t)(*reinterpret_cast<const unsigned short*>(&o2)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&o3)) << 16);
+    *reinterpret_cast<uint2*>(dst) = w;
+  } else {
+    dst[0] = o0;
+    dst[1] = o1;
+    dst[2] = o2;
+    dst[3] = o3;
+  }
+}
 
 // FUSE: the call is a whole decode step.  The CTA that owns the last partition of an item
 // also appends the item's new token: it patches the staged copy of the last K and V block in
@@ -55,9 +109,18 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     }
   }
   const int P = p.pb * BS;
+  MUX_TRACE_AT(0, 0);
 
-  griddep_wait();               // inputs may be written by the previous kernel of the stream
-  griddep_launch_dependents();  // the next kernel may start being scheduled behind this grid
+  // Programmatic dependent launch.  Normally nothing is read before every earlier kernel of the stream
+  // has completed.  With MUX_ATTN_EARLY_KV the caller vouches that the launch's index data and the KV
+  // blocks it names are not being written by the kernels just ahead of it, so this CTA resolves its item,
+  // fetches its block ids and fills its ring with the first KV blocks while those kernels drain; only
+  // q, the new K/V rows and every write (pool, workspace, out) stay behind the wait.
+  const bool early = (p.flags & MUX_ATTN_EARLY_KV) != 0;
+  if (!early) {
+    griddep_wait();
+    griddep_launch_dependents();  // the next kernel may start being scheduled behind this grid
+  }
   ItemDesc d = load_item<MIXED>(p, item);
   // The producer warp asks for the partition's first 32 block ids at once, before the context length
   // has arrived: entries below ceil(max_context_len / BS) exist in every block list whatever its length
@@ -65,16 +128,6 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   int spec_id = 0;
   if (warp == kConsumerWarps && lane < p.pb && part * p.pb + lane < (p.max_context_len + BS - 1) / BS)
     spec_id = d.bt_row[part * p.pb + lane];
-  // FUSE: the item's new K/V rows are requested at the same time (by every partition's producer warp;
-  // only the last partition uses them), so that no load latency is left when they are needed.
-  uint4 knew = make_uint4(0u, 0u, 0u, 0u);
-  uint2 vnew = make_uint2(0u, 0u);
-  if (FUSE && warp == kConsumerWarps) {
-    const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
-    const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
-    if (lane < 16) knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * lane);
-    vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + vo + 4 * lane);
-  }
   if (d.ctx < 0 || d.ctx > p.max_context_len) {
     if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
     d.ctx = d.ctx < 0 ? 0 : p.max_context_len;
@@ -93,14 +146,20 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_init(bars + 8 * i, 1);
       mbar_init(bars + 8 * (kMaxStages + i), 1);
     }
+    mbar_init(bars + 8 * (2 * kMaxStages), 1);  // the staged new rows are in shared memory
     mbar_init_fence();
   }
   __syncthreads();
+  MUX_TRACE_AT(1, 0);
 
   const int geff = info->geff;
   if (geff <= 0) return;
   T* out = static_cast<T*>(p.out);
   if (d.ctx == 0) {  // empty context: defined output (zeros), nothing to attend to
+    if (early) {
+      griddep_wait();
+      griddep_launch_dependents();
+    }
     if (tid < kHeadSize)
       for (int n = 0; n < geff; ++n) out[info->ooff[n] + tid] = from_float<T>(0.f);
     return;
@@ -122,36 +181,72 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       }
       ids[i] = id;
     }
-    if (FUSE && part == nparts - 1) {
-      // The decode step's new K/V rows of this item go to shared memory now (rotary applied to K),
-      // long before the consumer warp that appends them needs them.
-      if (p.rope_cache != nullptr) {
-        long long pos = min((long long)d.ctx - 1, p.rope_max_position - 1);
-        knew = rope_row16<T>(knew, lane, static_cast<const T*>(p.rope_cache) + pos * kHeadSize);
-      }
-      unsigned char* nr = smem + L.newrows;
-      if (lane < 16) *reinterpret_cast<uint4*>(nr + 16 * lane) = knew;
-      *reinterpret_cast<uint2*>(nr + 256 + 8 * lane) = vnew;
-    }
     __syncwarp();
-    if (lane == 0) {
-      const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
-      const unsigned char* vc = static_cast<const unsigned char*>(p.vc);
-      const int ntiles = 2 * nblk;
-      for (int j = 0; j < ntiles; ++j) {
-        const int stage = j % nst, use = j / nst;
-        if (use > 0)
-          mbar_wait(bars + 8 * (kMaxStages + stage), (use - 1) & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
+    MUX_TRACE_AT(10, kConsumerThreads);
+    const unsigned char* kc = static_cast<const unsigned char*>(p.kc);
+    const unsigned char* vc = static_cast<const unsigned char*>(p.vc);
+    const int ntiles = 2 * nblk;
+    const int first = min(ntiles, nst);  // the ring's first filling needs no free-stage wait
+    const int nl = p.prod_lanes;         // lanes that issue tiles (a divisor of nst): lane l takes tiles l, l + nl, ...
+    if (lane < nl) {
+      for (int j = lane; j < first; j += nl) {
         const long long bid = max(ids[j < nblk ? j : j - nblk], 0);
         const unsigned char* src = (j < nblk ? kc : vc) + bid * TILE;
-        mbar_arrive_expect_tx(bars + 8 * stage, TILE);
-        bulk_g2s(ring + stage * TILE, src, TILE, bars + 8 * stage);
+        mbar_arrive_expect_tx(bars + 8 * j, TILE);
+        bulk_g2s(ring + j * TILE, src, TILE, bars + 8 * j);
       }
     }
+    __syncwarp();
+    MUX_TRACE_AT(11, kConsumerThreads);
+    if (early) {
+      griddep_wait();
+      griddep_launch_dependents();
+    }
+    if (FUSE && part == nparts - 1 && lane >= 16) {
+      // The upper half-warp brings the decode step's new K/V rows of this item to shared memory (rotary
+      // applied to K) while lane 0 keeps issuing tiles; the consumer warp that appends them waits on
+      // their barrier.
+      const int l = lane - 16;
+      const long long ko = MIXED ? (long long)item * p.kn_s0 : (long long)d.seq * p.kn_s0 + (long long)d.kvh * p.kn_s1;
+      const long long vo = MIXED ? (long long)item * p.vn_s0 : (long long)d.seq * p.vn_s0 + (long long)d.kvh * p.vn_s1;
+      uint4 knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + ko + 8 * l);
+      const uint4 vnew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.v_new) + vo + 8 * l);
+      if (p.rope_cache != nullptr) {
+        long long pos = min((long long)d.ctx - 1, p.rope_max_position - 1);
+        knew = rope_row16<T>(knew, l, static_cast<const T*>(p.rope_cache) + pos * kHeadSize, 0xffff0000u);
+      }
+      unsigned char* nr = smem + L.newrows;
+      *reinterpret_cast<uint4*>(nr + 16 * l) = knew;
+      *reinterpret_cast<uint4*>(nr + 256 + 16 * l) = vnew;
+      __syncwarp(0xffff0000u);
+      if (l == 0) mbar_arrive(bars + 8 * (2 * kMaxStages));
+    }
+    if (lane < nl) {
+      // tiles nst + lane, nst + lane + nl, ...: stage and the parity of its previous use are kept incrementally
+      int stage = lane;
+      uint32_t parity = 0;
+      for (int j = nst + lane; j < ntiles; j += nl) {
+        const long long bid = max(ids[j < nblk ? j : j - nblk], 0);
+        const unsigned char* src = (j < nblk ? kc : vc) + bid * TILE;
+        mbar_wait(bars + 8 * (kMaxStages + stage), parity, p.status, MUX_DEV_WAIT_TIMEOUT);
+        mbar_arrive_expect_tx(bars + 8 * stage, TILE);
+        bulk_g2s(ring + stage * TILE, src, TILE, bars + 8 * stage);
+        stage += nl;
+        if (stage >= nst) {
+          stage -= nst;
+          parity ^= 1u;
+        }
+      }
+    }
+    MUX_TRACE_AT(12, kConsumerThreads);
     return;
   }
 
   // ---------------- consumer warps ----------------
+  if (early) {  // q (and everything written below) may depend on the kernels ahead
+    griddep_wait();
+    griddep_launch_dependents();
+  }
   const int g = lane >> 2, tq = lane & 3;
   float* S = reinterpret_cast<float*>(smem + L.s);
   const int SROW = L.srow;
@@ -198,6 +293,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     }
   }
 
+  MUX_TRACE_AT(2, 0);
   // ---- phase 1: logits ----
   {
     const int n0 = 2 * tq;
@@ -206,8 +302,10 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     for (int jb = warp; jb < nblk; jb += kConsumerWarps) {
       const int stage = jb % nst, use = jb / nst;
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
+      if (jb == 0) MUX_TRACE_AT(3, 0);
       const uint32_t tile = ring + stage * TILE;
       if (FUSE && appends && jb == jl) {  // K row of the new token: 16 pieces of 16 bytes
+        mbar_wait(bars + 8 * (2 * kMaxStages), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
         if (lane < 16) {
           const uint4 knew = *reinterpret_cast<const uint4*>(smem + L.newrows + 16 * lane);
           const uint32_t off = lane * CHUNK + ol * 16;
@@ -243,7 +341,9 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       if (lane == 0) mbar_arrive(bars + 8 * (kMaxStages + stage));
     }
   }
+  MUX_TRACE_AT(4, 0);
   named_bar_sync(1, kConsumerThreads);
+  MUX_TRACE_AT(5, 0);
 
   // ---- softmax over the unit ----
   for (int n = warp; n < geff; n += kConsumerWarps) {
@@ -265,6 +365,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     }
   }
   named_bar_sync(1, kConsumerThreads);
+  MUX_TRACE_AT(6, 0);
 
   // ---- phase 2: out^T[d][h] = sum_t V^T[d][t] P^T[t][h] ----
   float acc[8][4];
@@ -276,6 +377,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       const int j = nblk + jb;
       const int stage = j % nst, use = j / nst;
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
+      if (jb == 0) MUX_TRACE_AT(7, 0);
       const uint32_t tile = ring + stage * TILE;
       if (FUSE && appends && jb == jl) {  // V column of the new token: 128 single elements
         const uint2 vnew = *reinterpret_cast<const uint2*>(smem + L.newrows + 256 + 8 * lane);
@@ -325,6 +427,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     }
   }
 
+  MUX_TRACE_AT(8, 0);
   // ---- cross-warp reduction.  It reuses the buffer of the softmax weights, which the other
   // warps may still be reading: wait for all of them to finish phase 2 first.
   named_bar_sync(1, kConsumerThreads);
@@ -363,14 +466,11 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       }
     }
   }
+  MUX_TRACE_AT(9, 0);
 }
 
-// Merges the partitions of every item that has more than one.  One warp per (item, head tile, q head of the
-// group): the lanes reduce (max, sum) over the partitions, turn them into one weight per partition (kept in shared
-// memory) and then each lane accumulates four output elements from 16-byte loads, eight partitions in flight.
-constexpr int kMergeWarps = 4;
-constexpr int kMergeChunk = 128;  // partitions whose weights are staged at a time
-
+// Merges the partitions of every item that has more than one: one warp per (item, head tile, q head of
+// the group), see merge_one.
 template <typename T, int BS, bool MIXED>
 __global__ void __launch_bounds__(kMergeWarps * 32)
 paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
@@ -378,8 +478,10 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
   __shared__ float wts[kMergeWarps][kMergeChunk];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int P = p.pb * BS;
-  griddep_wait();
+  // This kernel reads nothing before its wait, so the kernel behind it may be scheduled at once: every
+  // kernel of this library waits for its predecessors itself before it touches what they write.
   griddep_launch_dependents();
+  griddep_wait();
   const long long unit = (long long)blockIdx.x * kMergeWarps + warp;
   if (unit >= p.num_items * p.head_tiles * p.gs) return;
   const int n = (int)(unit % p.gs);
@@ -396,51 +498,17 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
   __syncwarp();
   if (n >= info->geff) return;
   const long long slot0 = ((long long)item * p.head_tiles + htile) * p.max_parts;
-  float M = -INFINITY;
-  for (int k = lane; k < nparts; k += 32) M = fmaxf(M, p.ws_ml[((slot0 + k) * p.gs + n) * 2]);
-  M = warp_max(M);
-  float lsum = 0.f;
-  for (int k = lane; k < nparts; k += 32) {
-    const long long r = (slot0 + k) * p.gs + n;
-    lsum += p.ws_ml[r * 2 + 1] * __expf(p.ws_ml[r * 2] - M);
-  }
-  lsum = warp_sum(lsum);
-  const float inv = 1.f / lsum;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k0 = 0; k0 < nparts; k0 += kMergeChunk) {
-    const int cnt = min(kMergeChunk, nparts - k0);
-    for (int k = lane; k < cnt; k += 32)
-      wts[warp][k] = __expf(p.ws_ml[((slot0 + k0 + k) * p.gs + n) * 2] - M) * inv;
-    __syncwarp();
-    const float* src = p.ws_acc + ((slot0 + k0) * p.gs + n) * kHeadSize + 4 * lane;
-    const long long stride = (long long)p.gs * kHeadSize;
-#pragma unroll 8
-    for (int k = 0; k < cnt; ++k) {
-      const float4 a = *reinterpret_cast<const float4*>(src + k * stride);
-      const float w = wts[warp][k];
-      acc.x = fmaf(w, a.x, acc.x);
-      acc.y = fmaf(w, a.y, acc.y);
-      acc.z = fmaf(w, a.z, acc.z);
-      acc.w = fmaf(w, a.w, acc.w);
-    }
-    __syncwarp();
-  }
-  T* dst = static_cast<T*>(p.out) + info->ooff[n] + 4 * lane;
-  const T o0 = from_float<T>(acc.x), o1 = from_float<T>(acc.y), o2 = from_float<T>(acc.z), o3 = from_float<T>(acc.w);
-  if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
-    uint2 w;
-    w.x = (uint32_t)(*reinterpret_cast<const unsigned short*>(&o0)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&o1)) << 16);
-    w.y = (uint32_t)(*reinterpret_cast<const unsigned short*>(&o2)) | ((uint32_t)(*reinterpret_cast<const unsigned short*>(&o3)) << 16);
-    *reinterpret_cast<uint2*>(dst) = w;
-  } else {
-    dst[0] = o0;
-    dst[1] = o1;
-    dst[2] = o2;
-    dst[3] = o3;
-  }
+  merge_one<T>(p, slot0, n, nparts, info->ooff[n], wts[warp], lane);
 }
 
 // ------------------------------------------------------------------ host side
+
+#ifdef MUX_TRACE
+static unsigned long long* g_trace_ptr = nullptr;
+}  // namespace mux
+extern "C" void mux_debug_set_trace(void* p) { mux::g_trace_ptr = static_cast<unsigned long long*>(p); }
+namespace mux {
+#endif
 
 struct Plan {
   int pb, max_parts, gs, head_tiles, nst, smem;
@@ -457,9 +525,8 @@ static int default_stages(int block_size, int gs) {
 }
 
 static Plan make_plan(long long items, int group, int block_size, int max_context_len,
-                      int partition_size, int num_stages, int flags) {
+                      int partition_size, int num_stages) {
   Plan pl;
-  (void)flags;
   int psize = partition_size > 0 ? partition_size : 512;
   psize = std::max(block_size, (psize / block_size) * block_size);
   pl.pb = psize / block_size;
@@ -540,6 +607,10 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
   cfg.attrs = pdl;
   cfg.numAttrs = 1;
   prm.num_items = items;
+#ifdef MUX_TRACE
+  prm.trace = g_trace_ptr;
+  if (const char* e = getenv("MUX_PROD_LANES")) prm.prod_lanes = atoi(e);
+#endif
   if ((e = cudaLaunchKernelEx(&cfg, kern, prm)) != cudaSuccess) return record_cuda_error(e);
   if (pl.max_parts > 1) {
     static bool carve[kMaxDevicesTracked] = {};
@@ -596,7 +667,7 @@ static int validate(const mux_attn_args_t* a) {
   int st = check_common(a->dtype, a->head_size, a->block_size);
   if (st != MUX_OK) return st;
   if (a->num_seqs < 0 || a->num_q_heads <= 0 || a->num_kv_heads <= 0 || a->max_context_len < 0 ||
-      a->num_blocks <= 0 || a->partition_size < 0 || a->num_stages < 0)
+      a->num_blocks <= 0 || a->partition_size < 0 || a->num_stages < 0 || (a->flags & ~MUX_ATTN_EARLY_KV) != 0)
     return MUX_ERR_BAD_SHAPE;
   if (a->partition_size % a->block_size != 0) return MUX_ERR_BAD_SHAPE;
   if (a->num_q_heads % a->num_kv_heads != 0) return MUX_ERR_BAD_GROUP;
@@ -616,7 +687,7 @@ static int validate(const mux_attn_mixed_args_t* a) {
   int st = check_common(a->dtype, a->head_size, a->block_size);
   if (st != MUX_OK) return st;
   if (a->num_items < 0 || a->max_context_len < 0 || a->num_blocks <= 0 || a->partition_size < 0 ||
-      a->num_stages < 0)
+      a->num_stages < 0 || (a->flags & ~MUX_ATTN_EARLY_KV) != 0)
     return MUX_ERR_BAD_SHAPE;
   if (a->partition_size % a->block_size != 0) return MUX_ERR_BAD_SHAPE;
   if (a->max_group < 1 || a->max_group > 8) return MUX_ERR_BAD_GROUP;
@@ -633,12 +704,12 @@ static int validate(const mux_attn_mixed_args_t* a) {
 
 static Plan plan_of(const mux_attn_args_t* a) {
   return make_plan((long long)a->num_seqs * a->num_kv_heads, a->num_q_heads / a->num_kv_heads,
-                   a->block_size, a->max_context_len, a->partition_size, a->num_stages, a->flags);
+                   a->block_size, a->max_context_len, a->partition_size, a->num_stages);
 }
 
 static Plan plan_of(const mux_attn_mixed_args_t* a) {
   return make_plan(a->num_items, a->max_group, a->block_size, a->max_context_len, a->partition_size,
-                   a->num_stages, a->flags);
+                   a->num_stages);
 }
 
 static int check_workspace(const Plan& pl, const void* workspace, size_t workspace_bytes) {
@@ -669,10 +740,9 @@ struct NewRows {  // the decode step's new K/V rows; k == nullptr: plain attenti
   long long rope_max_position = 0;
 };
 
-static int validate_new_rows(const NewRows& n, int flags) {
+static int validate_new_rows(const NewRows& n) {
   if (n.k == nullptr && n.v == nullptr) return MUX_OK;
   if (n.k == nullptr || n.v == nullptr) return MUX_ERR_NULL_POINTER;
-  (void)flags;
   if (!aligned16(n.k) || !aligned16(n.v)) return MUX_ERR_MISALIGNED;
   if ((n.k_s0 & 7) || (n.k_s1 & 7) || (n.v_s0 & 7) || (n.v_s1 & 7)) return MUX_ERR_MISALIGNED;
   if (n.rope_cache != nullptr && (!aligned16(n.rope_cache) || n.rope_max_position <= 0)) return MUX_ERR_BAD_SHAPE;
@@ -683,7 +753,7 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
                       size_t workspace_bytes, void* cuda_stream) {
   int st = mux::validate(a);
   if (st != MUX_OK) return st;
-  if ((st = validate_new_rows(rows, a->flags)) != MUX_OK) return st;
+  if ((st = validate_new_rows(rows)) != MUX_OK) return st;
   if (a->num_seqs == 0) return MUX_OK;
   const long long items = (long long)a->num_seqs * a->num_kv_heads;
   const mux::Plan pl = mux::plan_of(a);
@@ -719,6 +789,8 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.max_parts = pl.max_parts;
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
+  prm.prod_lanes = 2;
+  prm.flags = a->flags;
   prm.k_new = rows.k;
   prm.v_new = rows.v;
   prm.kn_s0 = rows.k_s0;
@@ -751,6 +823,8 @@ int mux_decode_attention(const mux_decode_args_t* a, void* workspace, size_t wor
                          void* cuda_stream) {
   if (a == nullptr) return MUX_ERR_NULL_POINTER;
   if (a->attn.num_seqs > 0 && (a->k == nullptr || a->v == nullptr)) return MUX_ERR_NULL_POINTER;
+  // One new row per (sequence, kv head): with a shared block list the kv heads would all append to one slot.
+  if (a->attn.bt_head_stride == 0 && a->attn.num_kv_heads > 1) return MUX_ERR_BAD_SHAPE;
   mux::NewRows rows;
   rows.k = a->k;
   rows.v = a->v;
@@ -776,7 +850,7 @@ static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* 
                      size_t workspace_bytes, void* cuda_stream) {
   int st = mux::validate(a);
   if (st != MUX_OK) return st;
-  if ((st = validate_new_rows(rows, a->flags)) != MUX_OK) return st;
+  if ((st = validate_new_rows(rows)) != MUX_OK) return st;
   if (a->num_items == 0) return MUX_OK;
   const mux::Plan pl = mux::plan_of(a);
   if ((st = mux::plan_limits(pl, a->num_items)) != MUX_OK) return st;
@@ -805,6 +879,8 @@ static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* 
   prm.max_parts = pl.max_parts;
   prm.max_context_len = a->max_context_len;
   prm.nst = pl.nst;
+  prm.prod_lanes = 2;
+  prm.flags = a->flags;
   prm.k_new = rows.k;
   prm.v_new = rows.v;
   prm.kn_s0 = rows.k_s0;

@@ -40,15 +40,16 @@ __device__ __forceinline__ void rope_words(uint32_t& lo, uint32_t& hi, uint32_t 
   hi = pack2<T>(__fadd_rn(__fmul_rn(y.x, c.x), __fmul_rn(x.x, s.x)), __fadd_rn(__fmul_rn(y.y, c.y), __fmul_rn(x.y, s.y)));
 }
 
-// A 128-element row held by lanes 0..15 as 16-byte pieces (lane l: elements 8l .. 8l+7).  All 32
-// lanes must call; lanes >= 16 get their value back unchanged.
+// A 128-element row held by 16 lanes as 16-byte pieces (lane l: elements 8l .. 8l+7).  Every lane of
+// `mask` must call: the whole warp (lanes >= 16 get their value back unchanged), or one half-warp
+// (mask 0x0000ffff / 0xffff0000) with `lane` counted inside the half.
 template <typename T>
-__device__ __forceinline__ uint4 rope_row16(uint4 mine, int lane, const T* cache_row) {
+__device__ __forceinline__ uint4 rope_row16(uint4 mine, int lane, const T* cache_row, unsigned mask = 0xffffffffu) {
   uint4 other;
-  other.x = __shfl_xor_sync(0xffffffffu, mine.x, 8);
-  other.y = __shfl_xor_sync(0xffffffffu, mine.y, 8);
-  other.z = __shfl_xor_sync(0xffffffffu, mine.z, 8);
-  other.w = __shfl_xor_sync(0xffffffffu, mine.w, 8);
+  other.x = __shfl_xor_sync(mask, mine.x, 8);
+  other.y = __shfl_xor_sync(mask, mine.y, 8);
+  other.z = __shfl_xor_sync(mask, mine.z, 8);
+  other.w = __shfl_xor_sync(mask, mine.w, 8);
   if (lane >= 16) return mine;
   const int d0 = 8 * (lane & 7);
   const uint4 cs = *reinterpret_cast<const uint4*>(cache_row + d0);

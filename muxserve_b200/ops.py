@@ -132,7 +132,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                     max_context_len: int, *, num_kv_heads: Optional[int] = None,
                     partition_size: int = 0, num_stages: int = 0, flags: int = 0,
                     seq_rows: Optional[torch.Tensor] = None, units: Optional[torch.Tensor] = None,
-                    _new_kv=None, _rope=None) -> None:
+                    early_kv: bool = False, _new_kv=None, _rope=None) -> None:
     """Decode attention of one query token per sequence over the paged pool.
 
     ``q``/``out``: [S, Hq*128] or [S, Hq, 128].  ``block_tables``: int32
@@ -145,7 +145,13 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
     sequence ``s`` uses row ``seq_rows[s]`` of ``block_tables`` (``device_tables.DeviceBlockTables``).
     ``units`` (``work_units(host context lengths, H, partition_size)``, optional): the real (item, partition) pairs,
     so that no CTA is launched for a partition a sequence does not have; needs the same explicit ``partition_size``.
+    ``early_kv`` (``MUX_ATTN_EARLY_KV``): the caller states that neither the index tensors nor the KV blocks they name
+    are written by the one or two kernels directly ahead of this call in the stream (true for a layer's
+    ``decode_attention`` inside a decode step; NOT true right after ``reshape_and_cache`` of the same layer); the
+    launch then stages its first KV blocks while those kernels drain.
     """
+    if early_kv:
+        flags |= _lib.MUX_ATTN_EARLY_KV
     _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, head_mapping=head_mapping,
                   block_tables=block_tables, context_lens=context_lens)
     nb, bs = _pool(key_cache, value_cache)
@@ -213,6 +219,9 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
     else:
         k, v = _new_kv
         _require_cuda(k=k, v=v)
+        if bt_hs == 0 and H > 1:
+            raise ValueError("decode_attention appends one row per (sequence, kv head): every kv head needs its own "
+                             "block list ([S, H, max_blocks] block_tables)")
         Tk, Hk, k_ss, k_hs = _rows(k, "k")
         Tv, Hv, v_ss, v_hs = _rows(v, "v")
         if (Tk, Hk) != (S, H) or (Tv, Hv) != (S, H):
@@ -275,20 +284,21 @@ def work_units(item_context_lens, partition_size: int, device=None, num_kv_heads
 
     ``item_context_lens``: one length per (sequence, kv head) item — or one per sequence together with
     ``num_kv_heads`` (item = sequence * num_kv_heads + kv head).  Returns int32 ``item | partition << 24`` for every
-    real (item, partition) pair, fullest partitions first (a numpy array, or a tensor on ``device``)."""
+    real (item, partition) pair, fullest partitions first (a numpy array, or a tensor on ``device``).  An item with
+    an empty context gets its partition 0 too: that CTA writes the zeros the launch without a list would write."""
     import numpy as np
     ctx = np.asarray(item_context_lens, dtype=np.int64).reshape(-1)
     if num_kv_heads is not None:
         ctx = np.repeat(ctx, num_kv_heads)
     if partition_size <= 0:
         raise ValueError("the work list is built for an explicit partition size")
-    nparts = (np.maximum(ctx, 0) + partition_size - 1) // partition_size
+    nparts = np.maximum(1, (np.maximum(ctx, 0) + partition_size - 1) // partition_size)
     if ctx.size >= 1 << 24 or (nparts.size and int(nparts.max()) > 128):
         raise ValueError("too many items or partitions for a packed work list")
     item = np.repeat(np.arange(ctx.size, dtype=np.int64), nparts)
     first = np.cumsum(nparts) - nparts
     part = np.arange(item.size, dtype=np.int64) - np.repeat(first, nparts)
-    tokens = np.minimum(partition_size, ctx[item] - part * partition_size)
+    tokens = np.minimum(partition_size, np.maximum(ctx[item], 0) - part * partition_size)
     order = np.argsort(-tokens, kind="stable")
     packed = (item[order] | (part[order] << 24)).astype(np.uint32).view(np.int32).copy()
     return packed if device is None else torch.from_numpy(packed).to(device)
@@ -328,7 +338,7 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
                           max_context_len: int, max_group: int, *, partition_size: int = 0,
                           num_stages: int = 0, flags: int = 0, new_k: Optional[torch.Tensor] = None,
                           new_v: Optional[torch.Tensor] = None, cos_sin_cache: Optional[torch.Tensor] = None,
-                          units: Optional[torch.Tensor] = None) -> None:
+                          units: Optional[torch.Tensor] = None, early_kv: bool = False) -> None:
     """One launch for the decode batches of several models sharing the pool.
 
     Item ``i`` is one (sequence, kv head) of some model: q rows
@@ -340,7 +350,10 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
     ``item_context_len[i] - 1`` of its block list, as ``decode_attention`` does.
     ``units`` (``MixedPlan.units(layer, partition_size)``, int32) lists the real (item, partition) pairs so that no
     CTA is launched for a partition an item does not have; ``partition_size`` must then be the one the list was built for.
+    ``early_kv``: as in ``paged_attention``.
     """
+    if early_kv:
+        flags |= _lib.MUX_ATTN_EARLY_KV
     _require_cuda(out=out, q=q, key_cache=key_cache, value_cache=value_cache, block_tables=block_tables,
                   item_context_len=item_context_len, item_q_row=item_q_row, item_group=item_group,
                   item_scale=item_scale)
