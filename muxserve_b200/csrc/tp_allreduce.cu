@@ -37,7 +37,7 @@ namespace mux {
 constexpr int kArMaxWorld = MUX_TP_MAX_WORLD;
 constexpr int kArMaxCtas = 64;
 constexpr int kArThreads = 512;
-constexpr unsigned kArWaitLimit = 1u << 21;  // polls of ~1 us: a second or two
+constexpr unsigned kArWaitLimit = 1u << 23;  // polls of ~0.4 us: a few seconds
 
 struct ArCtrl {
   unsigned epoch;                            // launches completed on this rank

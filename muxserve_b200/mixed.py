@@ -50,6 +50,9 @@ class MixedPlan:
     layers: List[int]                # layer count of each model (in `order`)
     max_group: int
     max_context_len: int
+    item_context_len_host: np.ndarray = None   # the same lengths on the host (work lists, launch heuristics)
+    tp: int = 1                      # rows laid out for `tp` tensor-parallel ranks (see build_mixed_plan)
+    tp_rank: int = 0
 
     def active(self, layer: int):
         """(number of items, number of packed rows) that take part in `layer`."""
@@ -65,12 +68,16 @@ class MixedPlan:
         cache = self.__dict__.setdefault("_units", {})
         if key not in cache:
             from .ops import work_units
-            cache[key] = work_units(self.item_context_len[:n_items].cpu().numpy(), partition_size,
+            cache[key] = work_units(self.item_context_len_host[:n_items], partition_size,
                                     self.item_context_len.device)
         return cache[key]
 
 
-def build_mixed_plan(batches: Sequence[ModelBatch], device) -> MixedPlan:
+def build_mixed_plan(batches: Sequence[ModelBatch], device, tp: int = 1, tp_rank: int = 0) -> MixedPlan:
+    """``tp`` > 1: the batches hold the LOCAL heads of tensor-parallel rank ``tp_rank``; the packed q / out matrix is
+    then laid out as every model's full ``[S, tp * local q heads, D]`` with this rank's heads at their global
+    position, so that the sum of the ranks' ``out`` matrices (the TP all-reduce) is the models' whole output and
+    rows of other ranks' heads stay untouched (zero)."""
     order = sorted(range(len(batches)), key=lambda i: -batches[i].num_layers)
     ctx_all, row_all, grp_all, scl_all = [], [], [], []
     row_offset, item_offset, layers = [0], [0], []
@@ -84,10 +91,11 @@ def build_mixed_plan(batches: Sequence[ModelBatch], device) -> MixedPlan:
         ctx = b.context_lens.cpu().numpy().astype(np.int32)
         s_idx, h_idx = np.meshgrid(np.arange(S), np.arange(H), indexing="ij")
         ctx_all.append(np.repeat(ctx, H))
-        row_all.append((row_offset[-1] + s_idx * b.num_q_heads + h_idx * G).reshape(-1).astype(np.int32))
+        row_all.append((row_offset[-1] + s_idx * (b.num_q_heads * tp) + tp_rank * b.num_q_heads + h_idx * G)
+                       .reshape(-1).astype(np.int32))
         grp_all.append(np.full(S * H, G, dtype=np.int32))
         scl_all.append(np.full(S * H, b.scale, dtype=np.float32))
-        row_offset.append(row_offset[-1] + S * b.num_q_heads)
+        row_offset.append(row_offset[-1] + S * b.num_q_heads * tp)
         item_offset.append(item_offset[-1] + S * H)
         layers.append(b.num_layers)
     n_items = item_offset[-1]
@@ -102,18 +110,35 @@ def build_mixed_plan(batches: Sequence[ModelBatch], device) -> MixedPlan:
                      item_group=cat(grp_all, torch.int32), item_scale=cat(scl_all, torch.float32),
                      block_tables=tables, row_offset=row_offset, item_offset=item_offset, layers=layers,
                      max_group=max(b.group for b in batches),
-                     max_context_len=int(max(int(b.context_lens.max()) for b in batches)))
+                     max_context_len=int(max(int(b.context_lens.max()) for b in batches)),
+                     item_context_len_host=np.concatenate(ctx_all).astype(np.int64), tp=tp, tp_rank=tp_rank)
 
 
 def pack_rows(plan: MixedPlan, per_model: Sequence[torch.Tensor]) -> torch.Tensor:
-    """Concatenates per-model [S, Hq, D] tensors (caller's order) into the packed [rows, D] matrix."""
+    """Places per-model [S, Hq, D] tensors (caller's order) into the packed [rows, D] matrix (rows of other
+    tensor-parallel ranks' heads are zero)."""
+    if plan.tp == 1:
+        return torch.cat([per_model[i].reshape(-1, per_model[i].shape[-1]) for i in plan.order], dim=0)
+    D = per_model[0].shape[-1]
+    out = torch.zeros((plan.row_offset[-1], D), dtype=per_model[0].dtype, device=per_model[0].device)
+    for k, i in enumerate(plan.order):
+        S, Hq, _ = per_model[i].shape
+        view = out[plan.row_offset[k]:plan.row_offset[k + 1]].view(S, Hq * plan.tp, D)
+        view[:, plan.tp_rank * Hq:(plan.tp_rank + 1) * Hq] = per_model[i]
+    return out
+
+
+def pack_items(plan: MixedPlan, per_model: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Concatenates per-model [S, H, D] tensors (one row per (sequence, kv head), e.g. the new K / V rows) into the
+    [items, D] matrix in item order."""
     return torch.cat([per_model[i].reshape(-1, per_model[i].shape[-1]) for i in plan.order], dim=0)
 
 
 def unpack_rows(plan: MixedPlan, packed: torch.Tensor, batches: Sequence[ModelBatch]) -> List[torch.Tensor]:
-    """Views of the packed matrix per model, in the caller's order."""
+    """Views of the packed matrix per model (this rank's heads), in the caller's order."""
     out = [None] * len(batches)
     for k, i in enumerate(plan.order):
         b = batches[i]
-        out[i] = packed[plan.row_offset[k]:plan.row_offset[k + 1]].view(b.num_seqs, b.num_q_heads, packed.shape[-1])
+        view = packed[plan.row_offset[k]:plan.row_offset[k + 1]].view(b.num_seqs, b.num_q_heads * plan.tp, packed.shape[-1])
+        out[i] = view[:, plan.tp_rank * b.num_q_heads:(plan.tp_rank + 1) * b.num_q_heads]
     return out

@@ -18,6 +18,7 @@ from . import _lib
 from ._lib import AttnArgs, AttnMixedArgs, CacheWriteArgs, check, lib
 
 HEAD_SIZE = 128
+MAX_FUSED_NEW_TOKENS = 1   # new tokens per sequence that decode_attention appends in its own launch
 
 _DTYPES = {torch.float16: _lib.MUX_DTYPE_F16, torch.bfloat16: _lib.MUX_DTYPE_BF16}
 _workspaces = {}
@@ -304,12 +305,48 @@ def work_units(item_context_lens, partition_size: int, device=None, num_kv_heads
     return packed if device is None else torch.from_numpy(packed).to(device)
 
 
+def suggest_launch(item_context_lens, group: int, device=None, num_kv_heads: Optional[int] = None):
+    """(partition_size, num_stages) for a launch with a work list, from context lengths the HOST holds (one per
+    (sequence, kv head) item, or one per sequence together with ``num_kv_heads``).
+
+    Encodes what sweeps on B200 showed (148 SMs, six resident CTAs each at the default ring = 888 CTA places; one
+    CTA alone streams only ~25 GB/s, so a launch is fast when its work covers the places and no unit is much longer
+    than the rest):
+    * 512-token partitions unless the launch is much larger or much smaller than the places;
+    * one or two q heads per kv head and more than ~2 units per place at 512: the longest partition that still
+      gives every place a unit (no split at all for big batches: no partial results, no merge kernel);
+    * fewer than ~0.4 units per place at 512: the longest shorter partition that covers two thirds of the places;
+    * a launch that fills the places about once takes a 12-deep ring (four fuller CTAs per SM);
+    * grouped heads keep 512 and the default ring (their logits rows take shared memory in proportion)."""
+    import numpy as np
+    ctx = np.asarray(item_context_lens, dtype=np.int64).reshape(-1)
+    if num_kv_heads is not None:
+        ctx = np.repeat(ctx, num_kv_heads)
+    if group > 2 or ctx.size == 0:
+        return 512, 0
+    sms = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
+    places = 6 * sms
+    units = lambda psize: int(((np.maximum(ctx, 1) + psize - 1) // psize).sum())
+    top = 128
+    while top < min(4096, int(ctx.max())):
+        top *= 2
+    psize = min(512, top)
+    if units(512) > 2.2 * places:
+        for cand in (4096, 2048, 1024):
+            if cand <= top and units(cand) >= places:
+                psize = cand
+                break
+    elif units(512) < 0.4 * places:
+        psize = 128
+        for cand in (256,):
+            if units(cand) >= 0.68 * places:
+                psize = cand
+    stages = 12 if psize >= 512 and units(psize) <= 1.2 * places else 0
+    return psize, stages
+
+
 def suggest_partition_size(num_items: int, group: int, device=None) -> int:
-    """Partition size to build a work list for.  With the list's fullest-first order long partitions no longer
-    leave a tail, so launches with plenty of items (at least two per resident CTA place) and at most two q heads
-    per kv head do best with few or no splits (2048 tokens: no partial results, no merge kernel for contexts up to
-    2048); grouped heads keep 512 (their logits rows take shared memory in proportion to the partition), and so do
-    small launches, which need the split to fill the GPU."""
+    """Partition size when only the item count is known (see ``suggest_launch`` for the rule with the lengths)."""
     sms = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
     return 2048 if group <= 2 and num_items >= 2 * 6 * sms else 512
 

@@ -56,6 +56,7 @@ class TPAllReduce:
                 t = flexstore.rebuild_tensor(m)
                 check(lib().mux_tp_enable_peer_access(t.device.index), "tp_enable_peer_access")
                 self.peers.append(t)
+        self.slot_bytes = (nbytes - 8192) // 2      # what one message's exchange area may take (one-shot: world x message)
         self.comm = _lib.TpComm(world=self.world, rank=self.rank, buffer_bytes=nbytes)
         for r, t in enumerate(self.peers):
             self.comm.buffers[r] = t.data_ptr()

@@ -86,3 +86,23 @@ def test_prefill_work_units_group_tiles_of_a_prompt_and_start_with_the_longest()
     # within one (prompt, head) the last tile comes first
     rows = [(int(hq) >> 16) for s, hq in u if s == 2 and (int(hq) & 0xffff) == 0]
     assert rows == sorted(rows, reverse=True)
+
+
+def test_suggest_launch_follows_the_measured_rules(monkeypatch):
+    """Partition size and ring depth from host-held context lengths (no GPU: the SM count is faked)."""
+    import numpy as np
+    import torch
+    from muxserve_b200 import ops
+
+    class Props:
+        multi_processor_count = 148
+    monkeypatch.setattr(torch.cuda, "get_device_properties", lambda d: Props)
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    rng = np.random.default_rng(0)
+    big = rng.integers(128, 2049, size=64)                   # 64 sequences x 32 heads: far more units than CTA places
+    assert ops.suggest_launch(big, 1, num_kv_heads=32) == (2048, 0)          # no split at all
+    assert ops.suggest_launch(big, 1, num_kv_heads=4)[0] == 512              # a TP=8 shard: split to fill the GPU
+    small = np.clip(np.exp(rng.normal(np.log(256), 1.0, size=156)), 16, 4096).astype(int)
+    assert ops.suggest_launch(small, 1)[0] == 128                            # few short items: many short units
+    assert ops.suggest_launch(rng.integers(2048, 8193, size=2048), 8) == (512, 0)    # grouped heads keep 512
+    assert ops.suggest_launch([], 1) == (512, 0)
