@@ -1305,6 +1305,7 @@ def run_native_tp(env: Env):
     line["device_status"] = env.status | ops.device_status()
     if env.rank == 0:
         emit(line)
+    comm.close()
     env.dist.barrier()
     env.dist.destroy_process_group()
 

@@ -385,11 +385,13 @@ int mux_block_table_append(int32_t* tables, int64_t layer_stride, int64_t row_st
  * stores / loads and epoch flags, every wait bounded (MUX_DEV_WAIT_TIMEOUT when one runs out).
  * Every rank ends up with the same bits (fp32 sums in rank order).
  *
- * Set-up (host): each rank allocates one exchange buffer of mux_tp_allreduce_buffer_size() bytes,
- * 256-byte aligned and ZEROED, exports it (CUDA IPC), maps the other ranks' buffers, enables peer
- * access to their devices and synchronises with them once before the first call.  All ranks must make
+ * Set-up (host), with the rank's own GPU current throughout: each rank creates one exchange buffer of
+ * mux_tp_allreduce_buffer_size() bytes (mux_tp_buffer_create: its own zeroed allocation), exports it
+ * (mux_tp_buffer_export: a CUDA IPC handle, 64 bytes, to be carried to the other ranks by any host channel),
+ * imports the other ranks' handles (mux_tp_buffer_import: maps the peer's memory for THIS device and enables
+ * peer access to the peer's GPU) and synchronises with them once before the first call.  All ranks must make
  * the same sequence of calls (count, dtype, algo, num_ctas); calls of one communicator are ordered on
- * one stream per rank.  in == out is allowed.
+ * one stream per rank.  in == out is allowed.  Ranks of one process may pass plain device pointers.
  * ---------------------------------------------------------------------- */
 #define MUX_TP_MAX_WORLD 8
 #define MUX_TP_AUTO 0
@@ -404,8 +406,12 @@ typedef struct {
 } mux_tp_comm_t;
 
 size_t mux_tp_allreduce_buffer_size(int32_t world, size_t max_message_bytes);
-/* cudaDeviceEnablePeerAccess from the current device to peer_device (already enabled = ok). */
-int mux_tp_enable_peer_access(int32_t peer_device);
+#define MUX_TP_IPC_HANDLE_BYTES 64
+int mux_tp_buffer_create(size_t bytes, void** ptr);     /* on the current device, zeroed */
+int mux_tp_buffer_destroy(void* ptr);                   /* what mux_tp_buffer_create returned */
+int mux_tp_buffer_export(const void* ptr, unsigned char handle[MUX_TP_IPC_HANDLE_BYTES]);
+int mux_tp_buffer_import(const unsigned char handle[MUX_TP_IPC_HANDLE_BYTES], void** ptr);
+int mux_tp_buffer_release(void* ptr);                   /* what mux_tp_buffer_import returned */
 /* out = sum over ranks of in; count elements (multiple of 8) of dtype.  num_ctas 0 = heuristic (<= 64).
  * MUX_ERR_TOO_LARGE when the message does not fit the exchange buffers. */
 int mux_tp_allreduce(const mux_tp_comm_t* comm, const void* in, void* out, int64_t count, int32_t dtype,

@@ -26,7 +26,7 @@ MUX_ATTN_EARLY_KV = 1
 
 MUX_TP_AUTO, MUX_TP_ONE_SHOT, MUX_TP_TWO_SHOT = 0, 1, 2
 
-ABI_VERSION = 12
+ABI_VERSION = 13
 
 
 class CacheWriteArgs(C.Structure):
@@ -151,7 +151,11 @@ SIGNATURES = {
     "mux_block_table_append": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "mux_tp_allreduce_buffer_size": (C.c_size_t, [C.c_int32, C.c_size_t]),
-    "mux_tp_enable_peer_access": (C.c_int, [C.c_int32]),
+    "mux_tp_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "mux_tp_buffer_destroy": (C.c_int, [C.c_void_p]),
+    "mux_tp_buffer_export": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "mux_tp_buffer_import": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "mux_tp_buffer_release": (C.c_int, [C.c_void_p]),
     "mux_tp_allreduce": (C.c_int, [C.POINTER(TpComm), C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                    C.c_int32, C.c_void_p]),
     "mux_tp_allreduce_emulated": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p), C.c_int64, C.POINTER(C.c_void_p),

@@ -29,6 +29,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstring>
 
 #include "internal.h"
 
@@ -270,19 +271,74 @@ size_t mux_tp_allreduce_buffer_size(int32_t world, size_t max_message_bytes) {
   return mux::kArCtrlBytes + 2 * slot;
 }
 
-int mux_tp_enable_peer_access(int32_t peer_device) {
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return mux::record_cuda_error(e);
-  if (peer_device == dev) return MUX_OK;
-  int can = 0;
-  if ((e = cudaDeviceCanAccessPeer(&can, dev, peer_device)) != cudaSuccess) return mux::record_cuda_error(e);
-  if (!can) return mux::record_cuda_error(cudaErrorPeerAccessUnsupported);
-  e = cudaDeviceEnablePeerAccess(peer_device, 0);
-  if (e == cudaErrorPeerAccessAlreadyEnabled) {
-    (void)cudaGetLastError();  // not an error: clear it
-    return MUX_OK;
+int mux_tp_buffer_create(size_t bytes, void** ptr) {
+  if (ptr == nullptr || bytes == 0) return MUX_ERR_NULL_POINTER;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);  // its own allocation: an IPC handle names a whole allocation
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (p != nullptr) cudaFree(p);
+    return mux::record_cuda_error(e);
   }
+  *ptr = p;
+  return MUX_OK;
+}
+
+int mux_tp_buffer_destroy(void* ptr) {
+  if (ptr == nullptr) return MUX_OK;
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? MUX_OK : mux::record_cuda_error(e);
+}
+
+int mux_tp_buffer_export(const void* ptr, unsigned char handle[MUX_TP_IPC_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == MUX_TP_IPC_HANDLE_BYTES, "IPC handle size");
+  if (ptr == nullptr || handle == nullptr) return MUX_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(ptr));
+  if (e != cudaSuccess) return mux::record_cuda_error(e);
+  memcpy(handle, &h, sizeof(h));
+  return MUX_OK;
+}
+
+int mux_tp_buffer_import(const unsigned char handle[MUX_TP_IPC_HANDLE_BYTES], void** ptr) {
+  if (ptr == nullptr || handle == nullptr) return MUX_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  // Mapped into the address space of the CURRENT device (the one whose kernels will touch it), with peer
+  // access to the exporting GPU switched on as part of the mapping.
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return mux::record_cuda_error(e);
+  cudaPointerAttributes attr;
+  e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+    cudaIpcCloseMemHandle(p);
+    return mux::record_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevicePointer);
+  }
+  int dev = 0, can = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return mux::record_cuda_error(e);
+  if (attr.device != dev) {  // a peer GPU's memory: this device's kernels must be allowed to reach it
+    e = cudaDeviceCanAccessPeer(&can, dev, attr.device);
+    if (e != cudaSuccess || !can) {
+      cudaIpcCloseMemHandle(p);
+      return mux::record_cuda_error(e != cudaSuccess ? e : cudaErrorPeerAccessUnsupported);
+    }
+    e = cudaDeviceEnablePeerAccess(attr.device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      (void)cudaGetLastError();
+    } else if (e != cudaSuccess) {
+      cudaIpcCloseMemHandle(p);
+      return mux::record_cuda_error(e);
+    }
+  }
+  *ptr = p;
+  return MUX_OK;
+}
+
+int mux_tp_buffer_release(void* ptr) {
+  if (ptr == nullptr) return MUX_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
   return e == cudaSuccess ? MUX_OK : mux::record_cuda_error(e);
 }
 

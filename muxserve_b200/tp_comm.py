@@ -2,9 +2,8 @@
 
 The reference sums the row-parallel ``o_proj`` output over the TP group with NCCL
 (muxserve/flexserver/models/llama.py:131-137,162).  ``TPAllReduce`` sets up the exchange buffers
-that ``mux_tp_allreduce`` needs — one per rank, exported to the other ranks through CUDA IPC in the
-dictionary format FlexStore uses for its pool (muxserve/flexstore/manager.py:893-911) — and calls the
-kernel.  ``torch.distributed`` is only the plumbing that carries the IPC handles; the data path is the
+that ``mux_tp_allreduce`` needs — one per rank, exported to the other ranks through CUDA IPC (as FlexStore
+exports its pool to the model workers, muxserve/flexstore/manager.py:893-911) — and calls the kernel.  ``torch.distributed`` is only the plumbing that carries the IPC handles; the data path is the
 library's own kernel.
 """
 from __future__ import annotations
@@ -15,7 +14,7 @@ from typing import List, Optional
 import torch
 import torch.distributed as dist
 
-from . import _lib, flexstore
+from . import _lib
 from ._lib import check, lib
 
 _DTYPES = {torch.float16: _lib.MUX_DTYPE_F16, torch.bfloat16: _lib.MUX_DTYPE_BF16}
@@ -41,26 +40,43 @@ class TPAllReduce:
         self.device = torch.device(device)
         self.max_message_bytes = int(max_message_bytes)
         nbytes = buffer_size(self.world, self.max_message_bytes)
+        L = lib()
+        self._local = C.c_void_p()
+        self._imported = []
         with torch.cuda.device(self.device):
-            # its own allocation, zeroed: flags and epochs start at 0
-            self.local = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
-            torch.cuda.synchronize()
-            meta = flexstore.get_tensor_metadata(self.local)
-            metas: List[dict] = [None] * self.world
-            dist.all_gather_object(metas, meta, group=group)
-            self.peers: List[torch.Tensor] = []
-            for r, m in enumerate(metas):
+            check(L.mux_tp_buffer_create(nbytes, C.byref(self._local)), "tp_buffer_create")
+            handle = C.create_string_buffer(64)
+            check(L.mux_tp_buffer_export(self._local, handle), "tp_buffer_export")
+            handles: List[bytes] = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            ptrs = []
+            for r, raw in enumerate(handles):
                 if r == self.rank:
-                    self.peers.append(self.local)
+                    ptrs.append(self._local.value)
                     continue
-                t = flexstore.rebuild_tensor(m)
-                check(lib().mux_tp_enable_peer_access(t.device.index), "tp_enable_peer_access")
-                self.peers.append(t)
+                p = C.c_void_p()
+                check(L.mux_tp_buffer_import(raw, C.byref(p)), "tp_buffer_import")
+                self._imported.append(p)
+                ptrs.append(p.value)
         self.slot_bytes = (nbytes - 8192) // 2      # what one message's exchange area may take (one-shot: world x message)
         self.comm = _lib.TpComm(world=self.world, rank=self.rank, buffer_bytes=nbytes)
-        for r, t in enumerate(self.peers):
-            self.comm.buffers[r] = t.data_ptr()
+        for r, p in enumerate(ptrs):
+            self.comm.buffers[r] = p
         dist.barrier(group=group)      # every buffer is zeroed and mapped before anybody's first call
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees the local one (after every rank's last call: synchronise first)."""
+        L = lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for p in self._imported:
+                L.mux_tp_buffer_release(p)
+            self._imported = []
+            if dist.is_initialized():
+                dist.barrier(group=self.group)      # nobody still maps this rank's buffer
+            if self._local:
+                L.mux_tp_buffer_destroy(self._local)
+                self._local = C.c_void_p()
 
     def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, algo: int = _lib.MUX_TP_AUTO,
                    num_ctas: int = 0) -> torch.Tensor:

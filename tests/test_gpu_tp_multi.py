@@ -69,6 +69,7 @@ def _worker(rank, world, port, results):
     ok = ok and torch.equal(total.view(S, Hq, 128), whole)
     ok = ok and ops.device_status() == 0
     results.put((rank, bool(ok)))
+    comm.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -85,7 +86,7 @@ def test_peer_allreduce_and_head_sharding_on_real_ranks(built_lib):
     procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
     for p in procs:
         p.start()
-    got = dict(results.get(timeout=300) for _ in range(world))
+    got = dict(results.get(timeout=150) for _ in range(world))
     for p in procs:
         p.join(timeout=120)
     assert all(p.exitcode == 0 for p in procs)
