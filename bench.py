@@ -82,8 +82,11 @@ def emit(line: dict) -> None:
     print(json.dumps(line), file=out, flush=True)
 
 
+_T0 = time.perf_counter()
+
+
 def log(*a):
-    print("bench:", *a, file=sys.stderr, flush=True)
+    print(f"bench [{time.perf_counter() - _T0:6.1f} s]:", *a, file=sys.stderr, flush=True)
 
 
 def parse_args():
@@ -544,7 +547,8 @@ def run_decode(env: Env, pool: Pool, name: str, tp: int = 1, tp_rank: int = 0, h
     # ---- device-resident leg ----
     sampler = ClockSampler(env.local_rank) if headline else None
     run, per_step_launches, mode = env.capture(step, name)
-    ms_step, stats = env.timed(run, args.steps, args.warmup, sampler=sampler)
+    ms_step, stats = env.timed(run, args.steps, args.warmup, sampler=sampler,
+                               target_s=TARGET_REGION_S if headline else 0.5)
     clocks = sampler.stop() if sampler is not None else None
     res = {"ms_per_step": ms_step, "tokens_per_s": S / (ms_step * 1e-3), "timing": stats, "launch": mode,
            "kernels_per_step": per_step_launches, "resident_layers": L_res, "layers": L,
@@ -562,7 +566,7 @@ def run_decode(env: Env, pool: Pool, name: str, tp: int = 1, tp_rank: int = 0, h
         span = "timed region / launches (graph replay, one attention launch per layer)"
     else:
         run_a, _, _ = env.capture(lambda: step(allreduce=False, cache_write=False), name + " attention only")
-        ms_a, _ = env.timed(run_a, args.steps, 3, target_s=0.5)
+        ms_a, _ = env.timed(run_a, args.steps, 3, target_s=0.3)
         attn_ms = ms_a / L
         span = "a second timed region with only the attention launches of a step / launches"
         res["attention_only_ms_per_step"] = ms_a
@@ -1281,7 +1285,7 @@ def run_native_tp(env: Env):
         log("all-reduce sweep")
         tp["allreduce_sweep"] = allreduce_sweep(env, comm)
         others = {}
-        for n in ("c2", "c5", "c4"):
+        for n in ("c4", "c5", "c2"):          # bf16 workloads first: the pool is re-filled only once
             if n == name or WORKLOADS[n]["H"] % world != 0:
                 continue
             log("tp", n)
@@ -1303,11 +1307,13 @@ def run_native_tp(env: Env):
         del r
     line["tp"] = tp
     line["device_status"] = env.status | ops.device_status()
+    env.barrier()
     if env.rank == 0:
         emit(line)
-    comm.close()
-    env.dist.barrier()
-    env.dist.destroy_process_group()
+    # The step graphs hold captured NCCL kernels and the peers' mapped buffers; tearing communicators down
+    # under them has hung a run here for minutes.  Everything is measured and printed: leave without teardown.
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def main():

@@ -397,7 +397,7 @@ int mux_block_table_append(int32_t* tables, int64_t layer_stride, int64_t row_st
 #define MUX_TP_AUTO 0
 #define MUX_TP_ONE_SHOT 1                      /* each rank pushes its message to all, sums locally */
 #define MUX_TP_TWO_SHOT 2                      /* reduce-scatter by peer loads + all-gather by peer stores */
-#define MUX_TP_ONE_SHOT_MAX_BYTES (512 << 10)  /* MUX_TP_AUTO: largest message that goes one-shot */
+#define MUX_TP_ONE_SHOT_MAX_PUSH_BYTES (4 << 20)  /* MUX_TP_AUTO: one-shot while (world - 1) * message stays within this */
 typedef struct {
   int32_t world;                      /* 2 .. MUX_TP_MAX_WORLD */
   int32_t rank;
@@ -502,6 +502,33 @@ int mux_batch_scheduler_get_batch_decode_layered(
     int32_t* context_lens, int32_t num_contexts,
     int32_t* block_tables, int64_t block_tables_len,
     int64_t* slot_mapping, int64_t slot_mapping_len);
+/* The flattened descriptors of ONE fused attention launch per layer index over the decode batches of several
+ * colocated models (mux_paged_attention_mixed / mux_decode_attention_mixed), straight from their step builders.
+ * No counterpart in the reference, which runs every model in its own processes (muxserve/muxsched/scheduler.py:167-208);
+ * the tables are the ones csrc/batch_scheduler.cpp:156-169 would emit per model.  Call after every model's
+ * get_batch_info of the step.  Models are laid out deepest first (spans[] tells where), so the models that still
+ * have layer l are a prefix of the items and of the packed q / out rows.  With tp > 1 the schedulers hold the LOCAL
+ * heads of rank tp_rank and every model's rows are its full [sequences, tp * local q heads]: this rank's heads at
+ * their global position (the TP all-reduce of the ranks' out matrices is then the models' whole output). */
+typedef struct {
+  const mux_batch_scheduler_t* scheduler;
+  const int32_t* request_ids;   /* the model's decode batch, in batch order */
+  int32_t num_requests;
+  int32_t num_q_heads;          /* local; a multiple (<= 8x) of the scheduler's head count */
+  float scale;
+} mux_mixed_model_t;
+typedef struct {
+  int32_t model;                /* index into the caller's models[] */
+  int32_t first_item, num_items, first_row, num_rows, num_layers;
+} mux_mixed_span_t;
+/* totals[5] receives {items, rows, layers of the deepest model, largest group, max context length}.
+ * block_tables == NULL: sizing call (totals[0..3] and spans only).  Otherwise block_tables is
+ * [layers][items][max_blocks] int32 (unused entries 0) and the four item arrays have `items` entries. */
+int mux_batch_scheduler_get_batch_mixed(const mux_mixed_model_t* models, int32_t num_models, int32_t tp,
+                                        int32_t tp_rank, int32_t max_blocks, int32_t* item_context_len,
+                                        int32_t* item_q_row, int32_t* item_group, float* item_scale,
+                                        int32_t* block_tables, int64_t block_tables_len, mux_mixed_span_t* spans,
+                                        int32_t* totals);
 int mux_batch_scheduler_release_requests(mux_batch_scheduler_t* b, const int32_t* req_ids, int32_t n);
 /* batch_scheduler.h:88-92.  Each copies up to capacity entries and returns the full length. */
 int32_t mux_batch_scheduler_preempt_requests(const mux_batch_scheduler_t* b, int32_t* out, int32_t capacity);

@@ -130,6 +130,16 @@ class TpComm(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("buffers", C.c_void_p * 8), ("buffer_bytes", C.c_int64)]
 
 
+class MixedModel(C.Structure):
+    _fields_ = [("scheduler", C.c_void_p), ("request_ids", C.POINTER(C.c_int32)), ("num_requests", C.c_int32),
+                ("num_q_heads", C.c_int32), ("scale", C.c_float)]
+
+
+class MixedSpan(C.Structure):
+    _fields_ = [("model", C.c_int32), ("first_item", C.c_int32), ("num_items", C.c_int32), ("first_row", C.c_int32),
+                ("num_rows", C.c_int32), ("num_layers", C.c_int32)]
+
+
 _I32P = C.POINTER(C.c_int32)
 _I64P = C.POINTER(C.c_int64)
 
@@ -186,6 +196,9 @@ SIGNATURES = {
     "mux_batch_scheduler_get_batch_decode_layered": (C.c_int, [C.c_void_p, _I32P, C.c_int32, _I32P, C.c_int64,
                                                                _I32P, _I32P, C.c_int32, _I32P, C.c_int32,
                                                                _I32P, C.c_int64, _I64P, C.c_int64]),
+    "mux_batch_scheduler_get_batch_mixed": (C.c_int, [C.POINTER(MixedModel), C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                      _I32P, _I32P, _I32P, C.POINTER(C.c_float), _I32P, C.c_int64,
+                                                      C.POINTER(MixedSpan), _I32P]),
     "mux_batch_scheduler_release_requests": (C.c_int, [C.c_void_p, _I32P, C.c_int32]),
     "mux_batch_scheduler_preempt_requests": (C.c_int32, [C.c_void_p, _I32P, C.c_int32]),
     "mux_batch_scheduler_prompt_info": (C.c_int32, [C.c_void_p, _I32P, C.c_int32]),

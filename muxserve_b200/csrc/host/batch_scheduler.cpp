@@ -341,4 +341,85 @@ int mux_batch_scheduler_request_state(const mux_batch_scheduler_t* b, int32_t re
   return MUX_OK;
 }
 
+int mux_batch_scheduler_get_batch_mixed(const mux_mixed_model_t* models, int32_t num_models, int32_t tp,
+                                        int32_t tp_rank, int32_t max_blocks, int32_t* item_context_len,
+                                        int32_t* item_q_row, int32_t* item_group, float* item_scale,
+                                        int32_t* block_tables, int64_t block_tables_len, mux_mixed_span_t* spans,
+                                        int32_t* totals) {
+  if (models == nullptr || spans == nullptr || totals == nullptr) return MUX_ERR_NULL_POINTER;
+  if (num_models <= 0 || tp < 1 || tp_rank < 0 || tp_rank >= tp || max_blocks < 0) return MUX_ERR_BAD_SHAPE;
+  // ---- everything that can fail, and the sizes ----
+  std::vector<int32_t> order((size_t)num_models);
+  for (int32_t m = 0; m < num_models; ++m) {
+    const mux_mixed_model_t& md = models[m];
+    if (md.scheduler == nullptr) return MUX_ERR_BAD_HANDLE;
+    if (md.num_requests < 0 || (md.num_requests > 0 && md.request_ids == nullptr)) return MUX_ERR_BAD_SHAPE;
+    const int32_t H = md.scheduler->H;
+    if (md.num_q_heads <= 0 || md.num_q_heads % H != 0 || md.num_q_heads / H > 8) return MUX_ERR_BAD_GROUP;
+    for (int32_t i = 0; i < md.num_requests; ++i) {
+      const Seq* sq = md.scheduler->find(md.request_ids[i]);
+      if (sq == nullptr) return MUX_ERR_UNKNOWN_REQUEST;
+      if (sq->outputs.empty() || sq->phys_blocks < 1) return MUX_ERR_BAD_SHAPE;  // decode rows only
+      if (sq->phys_blocks > max_blocks) return MUX_ERR_BUFFER_TOO_SMALL;
+    }
+    order[(size_t)m] = m;
+  }
+  // deepest model first: the models that still have layer l are always a prefix of the items and rows
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int32_t a, int32_t b) { return models[a].scheduler->L > models[b].scheduler->L; });
+  int64_t items = 0, rows = 0;
+  int32_t max_layers = 0, max_ctx = 0, max_group = 1;
+  for (int32_t k = 0; k < num_models; ++k) {
+    const mux_mixed_model_t& md = models[order[(size_t)k]];
+    mux_mixed_span_t& sp = spans[k];
+    sp.model = order[(size_t)k];
+    sp.first_item = (int32_t)items;
+    sp.num_items = md.num_requests * md.scheduler->H;
+    sp.first_row = (int32_t)rows;
+    sp.num_rows = md.num_requests * md.num_q_heads * tp;
+    sp.num_layers = md.scheduler->L;
+    items += sp.num_items;
+    rows += sp.num_rows;
+    max_layers = std::max(max_layers, sp.num_layers);
+    max_group = std::max(max_group, md.num_q_heads / md.scheduler->H);
+  }
+  if (items > 0x7fffffffLL || rows > 0x7fffffffLL) return MUX_ERR_TOO_LARGE;
+  totals[0] = (int32_t)items;
+  totals[1] = (int32_t)rows;
+  totals[2] = max_layers;
+  totals[3] = max_group;
+  if (block_tables == nullptr) {  // sizing call
+    totals[4] = 0;
+    return MUX_OK;
+  }
+  if (!item_context_len || !item_q_row || !item_group || !item_scale) return MUX_ERR_NULL_POINTER;
+  if ((int64_t)max_layers * items * max_blocks > block_tables_len) return MUX_ERR_BUFFER_TOO_SMALL;
+  std::memset(block_tables, 0, (size_t)((int64_t)max_layers * items * max_blocks) * sizeof(int32_t));
+  for (int32_t k = 0; k < num_models; ++k) {
+    const mux_mixed_model_t& md = models[spans[k].model];
+    const mux_batch_scheduler* b = md.scheduler;
+    const int32_t H = b->H, G = md.num_q_heads / H;
+    const int64_t LH = (int64_t)b->L * H;
+    for (int32_t i = 0; i < md.num_requests; ++i) {
+      const Seq* sq = b->find(md.request_ids[i]);
+      max_ctx = std::max(max_ctx, sq->context_len);
+      for (int32_t h = 0; h < H; ++h) {
+        const int64_t item = spans[k].first_item + (int64_t)i * H + h;
+        item_context_len[item] = sq->context_len;
+        // this rank's heads sit at their global position inside the model's [S, tp * local heads] rows
+        item_q_row[item] = spans[k].first_row + i * (md.num_q_heads * tp) + tp_rank * md.num_q_heads + h * G;
+        item_group[item] = G;
+        item_scale[item] = md.scale;
+        for (int32_t l = 0; l < b->L; ++l) {
+          int32_t* dst = block_tables + ((int64_t)l * items + item) * max_blocks;
+          const int32_t* src = sq->table.data() + (int64_t)l * H + h;
+          for (int32_t j = 0; j < sq->phys_blocks; ++j) dst[j] = src[(int64_t)j * LH];
+        }
+      }
+    }
+  }
+  totals[4] = max_ctx;
+  return MUX_OK;
+}
+
 }  // extern "C"

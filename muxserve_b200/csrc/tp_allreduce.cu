@@ -224,9 +224,10 @@ __global__ void __launch_bounds__(kArThreads) tp_allreduce_emulated_kernel(const
   allreduce_body<T>(p, blockIdx.y, blockIdx.x);
 }
 
-static int pick_algo(int algo, size_t bytes) {
+static int pick_algo(int algo, int world, size_t bytes) {
   if (algo == MUX_TP_ONE_SHOT || algo == MUX_TP_TWO_SHOT) return algo;
-  return bytes <= (size_t)MUX_TP_ONE_SHOT_MAX_BYTES ? MUX_TP_ONE_SHOT : MUX_TP_TWO_SHOT;
+  // one-shot sends the whole message to every peer: cheapest in latency while that traffic stays small
+  return (size_t)(world - 1) * bytes <= (size_t)MUX_TP_ONE_SHOT_MAX_PUSH_BYTES ? MUX_TP_ONE_SHOT : MUX_TP_TWO_SHOT;
 }
 
 static int pick_ctas(int num_ctas, int algo, int world, long long nvec) {
@@ -249,7 +250,7 @@ static int fill_params(ArParams& prm, int world, void* const* buffers, long long
     prm.buf[q] = static_cast<unsigned char*>(buffers[q]);
   }
   const size_t bytes = (size_t)count * 2;
-  prm.algo = pick_algo(algo, bytes);
+  prm.algo = pick_algo(algo, world, bytes);
   prm.world = world;
   prm.nvec = count / 8;
   prm.slot_bytes = (buffer_bytes - (long long)kArCtrlBytes) / 2 / 256 * 256;

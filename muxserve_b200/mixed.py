@@ -114,6 +114,45 @@ def build_mixed_plan(batches: Sequence[ModelBatch], device, tp: int = 1, tp_rank
                      item_context_len_host=np.concatenate(ctx_all).astype(np.int64), tp=tp, tp_rank=tp_rank)
 
 
+def plan_from_schedulers(models, device, max_blocks: int, tp: int = 1, tp_rank: int = 0) -> MixedPlan:
+    """The same plan built by the host library straight from the models' step builders
+    (``mux_batch_scheduler_get_batch_mixed``): ``models`` is a list of ``(BatchScheduler, request ids of its decode
+    batch, local q heads, softmax scale)``; call after every scheduler's ``get_batch_info`` of the step.
+    ``plan.order`` indexes that list, deepest model first."""
+    import ctypes as C
+
+    from . import _lib
+    n = len(models)
+    arr = (_lib.MixedModel * n)()
+    keep = []
+    for m, (sched, req_ids, num_q_heads, scale) in enumerate(models):
+        ids = np.ascontiguousarray(np.asarray(req_ids, dtype=np.int32))
+        keep.append(ids)
+        arr[m] = _lib.MixedModel(sched._h, _lib.i32p(ids), ids.size, int(num_q_heads), float(scale))
+    spans = (_lib.MixedSpan * n)()
+    totals = np.zeros(5, dtype=np.int32)
+    L = _lib.lib()
+    _lib.check(L.mux_batch_scheduler_get_batch_mixed(arr, n, tp, tp_rank, max_blocks, None, None, None, None, None, 0,
+                                                     spans, _lib.i32p(totals)), "get_batch_mixed (sizes)")
+    items, rows, layers_max, max_group = (int(x) for x in totals[:4])
+    ctx = np.empty(items, dtype=np.int32)
+    row = np.empty(items, dtype=np.int32)
+    grp = np.empty(items, dtype=np.int32)
+    scl = np.empty(items, dtype=np.float32)
+    tables = np.empty((layers_max, items, max_blocks), dtype=np.int32)
+    _lib.check(L.mux_batch_scheduler_get_batch_mixed(arr, n, tp, tp_rank, max_blocks, _lib.i32p(ctx), _lib.i32p(row),
+                                                     _lib.i32p(grp), scl.ctypes.data_as(C.POINTER(C.c_float)),
+                                                     _lib.i32p(tables), tables.size, spans, _lib.i32p(totals)),
+               "get_batch_mixed")
+    up = lambda a: torch.from_numpy(a).to(device)
+    return MixedPlan(order=[spans[k].model for k in range(n)], item_context_len=up(ctx), item_q_row=up(row),
+                     item_group=up(grp), item_scale=up(scl), block_tables=up(tables),
+                     row_offset=[spans[k].first_row for k in range(n)] + [rows],
+                     item_offset=[spans[k].first_item for k in range(n)] + [items],
+                     layers=[spans[k].num_layers for k in range(n)], max_group=max_group,
+                     max_context_len=int(totals[4]), item_context_len_host=ctx.astype(np.int64), tp=tp, tp_rank=tp_rank)
+
+
 def pack_rows(plan: MixedPlan, per_model: Sequence[torch.Tensor]) -> torch.Tensor:
     """Places per-model [S, Hq, D] tensors (caller's order) into the packed [rows, D] matrix (rows of other
     tensor-parallel ranks' heads are zero)."""
