@@ -254,10 +254,15 @@ int mux_paged_attention_mixed(const mux_attn_mixed_args_t* args, void* workspace
  * the slot csrc/batch_scheduler.h:58-67 puts in slot_mapping, and attention runs over
  * all context_len tokens.  Same results as mux_reshape_and_cache followed by
  * mux_paged_attention, bit for bit.
+ * A step may append several tokens per sequence (new_tokens, up to MUX_MAX_FUSED_NEW_TOKENS; the reference
+ * itself appends one): k / v then hold new_tokens consecutive rows per sequence, token-major, for positions
+ * context_len - new_tokens .. context_len - 1 (context_len counts them all), and the one query of the sequence
+ * attends over everything.  With rotary, new key j is rotated at its own position, the query at context_len - 1.
  * ---------------------------------------------------------------------- */
+#define MUX_MAX_FUSED_NEW_TOKENS 16
 typedef struct {
   mux_attn_args_t attn;
-  const void* k;            /* [num_seqs, num_kv_heads, head_size] new rows (strided views allowed) */
+  const void* k;            /* [num_seqs * new_tokens, num_kv_heads, head_size] new rows (strided views allowed) */
   const void* v;
   int64_t k_seq_stride;     /* elements */
   int64_t k_head_stride;
@@ -265,6 +270,8 @@ typedef struct {
   int64_t v_head_stride;
   const void* cos_sin_cache; /* NULL, or rotary cache [max_position][64 cos | 64 sin] in the tensor dtype: q and the */
   int64_t max_position;      /* new k are rotated at position context_len - 1 first (see mux_rotary_embedding) */
+  int32_t new_tokens;        /* rows per (sequence, kv head); 0 means 1 */
+  int32_t reserved;
 } mux_decode_args_t;
 
 /* workspace: mux_paged_attention_workspace_size(&args->attn) */
@@ -273,12 +280,14 @@ int mux_decode_attention(const mux_decode_args_t* args, void* workspace, size_t 
 
 typedef struct {
   mux_attn_mixed_args_t attn;
-  const void* k;            /* [num_items, head_size]: one new row per item */
+  const void* k;            /* [num_items * new_tokens, head_size]: new_tokens consecutive rows per item */
   const void* v;
   int64_t k_row_stride;     /* elements */
   int64_t v_row_stride;
   const void* cos_sin_cache; /* as in mux_decode_args_t; one cache for all models of the launch */
   int64_t max_position;
+  int32_t new_tokens;        /* as in mux_decode_args_t */
+  int32_t reserved;
 } mux_decode_mixed_args_t;
 
 /* workspace: mux_paged_attention_mixed_workspace_size(&args->attn) */

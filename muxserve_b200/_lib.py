@@ -26,7 +26,7 @@ MUX_ATTN_EARLY_KV = 1
 
 MUX_TP_AUTO, MUX_TP_ONE_SHOT, MUX_TP_TWO_SHOT = 0, 1, 2
 
-ABI_VERSION = 13
+ABI_VERSION = 14
 
 
 class CacheWriteArgs(C.Structure):
@@ -86,6 +86,7 @@ class DecodeArgs(C.Structure):
         ("k_seq_stride", C.c_int64), ("k_head_stride", C.c_int64),
         ("v_seq_stride", C.c_int64), ("v_head_stride", C.c_int64),
         ("cos_sin_cache", C.c_void_p), ("max_position", C.c_int64),
+        ("new_tokens", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -94,6 +95,7 @@ class DecodeMixedArgs(C.Structure):
         ("attn", AttnMixedArgs), ("k", C.c_void_p), ("v", C.c_void_p),
         ("k_row_stride", C.c_int64), ("v_row_stride", C.c_int64),
         ("cos_sin_cache", C.c_void_p), ("max_position", C.c_int64),
+        ("new_tokens", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

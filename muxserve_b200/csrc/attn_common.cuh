@@ -50,6 +50,7 @@ struct AttnParams {
   const void* k_new;
   const void* v_new;
   long long kn_s0, kn_s1, vn_s0, vn_s1;  // single model: seq, head strides; mixed: s0 = item (row) stride
+  int new_tokens;                        // fused decode step: rows appended per (sequence, kv head), 1..16
   const void* rope_cache;                // fused decode step only: [max_position][64 cos | 64 sin], or nullptr
   long long rope_max_position;
   long long num_items;                   // (sequence, kv head) items of the launch

@@ -82,10 +82,14 @@ __device__ __forceinline__ void merge_one(const AttnParams& p, long long slot0, 
   }
 }
 
-// FUSE: the call is a whole decode step.  The CTA that owns the last partition of an item
-// also appends the item's new token: it patches the staged copy of the last K and V block in
-// shared memory with the new rows (so the attention sees them) and writes them to the pool.
-template <typename T, int BS, bool MIXED, bool FUSE>
+// FUSE != 0: the call is a whole decode step, the new tokens' K/V rows are appended by the launch itself.
+//   1  one new token per sequence (what the reference's decode step appends): the CTA that owns the item's last
+//      partition patches the staged copy of the last K and V block in shared memory with the new rows, so the
+//      attention sees them, and writes them to the pool; the rows reach shared memory beside the KV stream.
+//   2  several new tokens: the producer warp of the CTA whose partition holds their positions writes the rows
+//      into the pool first (rotary applied to K) and only then issues the bulk copies of the blocks that received
+//      them; about 1 us more on that CTA's path, no extra shared memory whatever the token count.
+template <typename T, int BS, bool MIXED, int FUSE>
 __global__ void __launch_bounds__(kThreads, 6)  // six CTAs per SM: at most 64 registers per thread
 paged_attn_kernel(const __grid_constant__ AttnParams p) {
   constexpr int TILE = kHeadSize * BS * 2;       // bytes of one K or V block
@@ -128,9 +132,9 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   int spec_id = 0;
   if (warp == kConsumerWarps && lane < p.pb && part * p.pb + lane < (p.max_context_len + BS - 1) / BS)
     spec_id = d.bt_row[part * p.pb + lane];
-  if (d.ctx < 0 || d.ctx > p.max_context_len) {
-    if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
-    d.ctx = d.ctx < 0 ? 0 : p.max_context_len;
+  if (d.ctx < 0 || d.ctx > p.max_context_len || (FUSE == 2 && d.ctx > 0 && d.ctx < p.new_tokens)) {
+    if (tid == 0) atomicOr(p.status, MUX_DEV_BAD_CONTEXT);  // (a decode step's context counts its new tokens)
+    d.ctx = d.ctx < 0 ? 0 : min(max(d.ctx, FUSE == 2 ? p.new_tokens : 0), p.max_context_len);
   }
   const int nparts = (d.ctx + P - 1) / P;
   if (part >= nparts && !(d.ctx == 0 && part == 0)) return;
@@ -188,10 +192,21 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
     const int ntiles = 2 * nblk;
     const int first = min(ntiles, nst);  // the ring's first filling needs no free-stage wait
     const int nl = p.prod_lanes;         // lanes that issue tiles (a divisor of nst): lane l takes tiles l, l + nl, ...
+    // FUSE == 2: the new tokens' positions that fall into this partition, [lo, hi), and the first block they touch.
+    // In the ring's first filling (any order is fine there) the tiles of earlier blocks go out at once; those of
+    // the blocks that receive new rows follow when the rows are in the pool.
+    int lo = 0, hi = 0;
+    if (FUSE == 2) {
+      lo = max(d.ctx - p.new_tokens, tok0);
+      hi = min(d.ctx, tok0 + ntok);
+    }
+    const bool has_new = FUSE == 2 && lo < hi;
+    const int jb_new = has_new ? (lo - tok0) / BS : nblk;
     if (lane < nl) {
       for (int j = lane; j < first; j += nl) {
-        const long long bid = max(ids[j < nblk ? j : j - nblk], 0);
-        const unsigned char* src = (j < nblk ? kc : vc) + bid * TILE;
+        const int jb = j < nblk ? j : j - nblk;
+        if (jb >= jb_new) continue;
+        const unsigned char* src = (j < nblk ? kc : vc) + (long long)max(ids[jb], 0) * TILE;
         mbar_arrive_expect_tx(bars + 8 * j, TILE);
         bulk_g2s(ring + j * TILE, src, TILE, bars + 8 * j);
       }
@@ -202,7 +217,55 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       griddep_wait();
       griddep_launch_dependents();
     }
-    if (FUSE && part == nparts - 1 && lane >= 16) {
+    if (has_new) {
+      // ---- append: K rows as 16 pieces of 16 bytes (two rows per pass, one per half-warp), V rows as 128 single
+      // elements (the pool keeps V token-minor), four per lane ----
+      const int first_new = d.ctx - p.new_tokens;
+      const int half = lane >> 4, l = lane & 15;
+      unsigned char* kcw = static_cast<unsigned char*>(const_cast<void*>(p.kc));
+      unsigned short* vcw = reinterpret_cast<unsigned short*>(const_cast<void*>(p.vc));
+      for (int r0 = lo; r0 < hi; r0 += 2) {
+        const bool live = r0 + half < hi;
+        const int r = live ? r0 + half : hi - 1;  // the idle half still takes part in the shuffles of the rotation
+        const long long row = MIXED ? ((long long)item * p.new_tokens + (r - first_new)) * p.kn_s0
+                                    : ((long long)d.seq * p.new_tokens + (r - first_new)) * p.kn_s0 + (long long)d.kvh * p.kn_s1;
+        uint4 knew = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.k_new) + row + 8 * l);
+        if (p.rope_cache != nullptr) {
+          const long long pos = min((long long)r, p.rope_max_position - 1);
+          knew = rope_row16<T>(knew, l, static_cast<const T*>(p.rope_cache) + pos * kHeadSize);
+        }
+        const int id = ids[(r - tok0) / BS];
+        if (live && id >= 0)
+          *reinterpret_cast<uint4*>(kcw + (long long)id * TILE + l * CHUNK + ((r - tok0) % BS) * 16) = knew;
+      }
+      for (int r = lo; r < hi; ++r) {
+        const long long row = MIXED ? ((long long)item * p.new_tokens + (r - first_new)) * p.vn_s0
+                                    : ((long long)d.seq * p.new_tokens + (r - first_new)) * p.vn_s0 + (long long)d.kvh * p.vn_s1;
+        const uint2 vnew = *reinterpret_cast<const uint2*>(static_cast<const T*>(p.v_new) + row + 4 * lane);
+        const int id = ids[(r - tok0) / BS];
+        if (id >= 0) {
+          unsigned short* dst = vcw + (long long)id * (TILE / 2) + (4 * lane) * BS + (r - tok0) % BS;
+          dst[0] = (unsigned short)(vnew.x & 0xffffu);
+          dst[BS] = (unsigned short)(vnew.x >> 16);
+          dst[2 * BS] = (unsigned short)(vnew.y & 0xffffu);
+          dst[3 * BS] = (unsigned short)(vnew.y >> 16);
+        }
+      }
+      // the rows must be in the pool before the bulk copies (another proxy) of their blocks read it: every lane
+      // orders its own writes before later async-proxy accesses, the warp barrier carries that to the issuing lanes
+      fence_proxy_async_global();
+      __syncwarp();
+    }
+    if (has_new && lane < nl) {
+      for (int j = lane; j < first; j += nl) {
+        const int jb = j < nblk ? j : j - nblk;
+        if (jb < jb_new) continue;
+        const unsigned char* src = (j < nblk ? kc : vc) + (long long)max(ids[jb], 0) * TILE;
+        mbar_arrive_expect_tx(bars + 8 * j, TILE);
+        bulk_g2s(ring + j * TILE, src, TILE, bars + 8 * j);
+      }
+    }
+    if (FUSE == 1 && part == nparts - 1 && lane >= 16) {
       // The upper half-warp brings the decode step's new K/V rows of this item to shared memory (rotary
       // applied to K) while lane 0 keeps issuing tiles; the consumer warp that appends them waits on
       // their barrier.
@@ -255,7 +318,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
   // has staged the new rows in shared memory by then).
   const int new_local = d.ctx - 1 - tok0;  // the appended token's index inside this partition
   const int jl = new_local / BS, ol = new_local % BS;
-  const bool appends = FUSE && part == nparts - 1 && (jl & (kConsumerWarps - 1)) == warp;
+  const bool appends = FUSE == 1 && part == nparts - 1 && (jl & (kConsumerWarps - 1)) == warp;
   const int* ids_c = reinterpret_cast<const int*>(smem + L.ids);
   // Rotary embedding of the decode step: the query and the new key sit at position ctx - 1.
   const T* rope_row = nullptr;
@@ -304,7 +367,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       if (jb == 0) MUX_TRACE_AT(3, 0);
       const uint32_t tile = ring + stage * TILE;
-      if (FUSE && appends && jb == jl) {  // K row of the new token: 16 pieces of 16 bytes
+      if (FUSE == 1 && appends && jb == jl) {  // K row of the new token: 16 pieces of 16 bytes
         mbar_wait(bars + 8 * (2 * kMaxStages), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
         if (lane < 16) {
           const uint4 knew = *reinterpret_cast<const uint4*>(smem + L.newrows + 16 * lane);
@@ -379,7 +442,7 @@ paged_attn_kernel(const __grid_constant__ AttnParams p) {
       mbar_wait(bars + 8 * stage, use & 1, p.status, MUX_DEV_WAIT_TIMEOUT);
       if (jb == 0) MUX_TRACE_AT(7, 0);
       const uint32_t tile = ring + stage * TILE;
-      if (FUSE && appends && jb == jl) {  // V column of the new token: 128 single elements
+      if (FUSE == 1 && appends && jb == jl) {  // V column of the new token: 128 single elements
         const uint2 vnew = *reinterpret_cast<const uint2*>(smem + L.newrows + 256 + 8 * lane);
         const unsigned short e[4] = {(unsigned short)(vnew.x & 0xffffu), (unsigned short)(vnew.x >> 16),
                                      (unsigned short)(vnew.y & 0xffffu), (unsigned short)(vnew.y >> 16)};
@@ -585,7 +648,7 @@ static int ensure_smem(K kern, int smem, int dev, int* granted) {
   return MUX_OK;
 }
 
-template <typename T, int BS, bool MIXED, bool FUSE>
+template <typename T, int BS, bool MIXED, int FUSE>
 static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaStream_t stream, int num_units) {
   int dev = 0;
   DeviceInfo di;
@@ -632,10 +695,11 @@ static int launch_typed(AttnParams& prm, const Plan& pl, long long items, cudaSt
 template <bool MIXED>
 static int launch(AttnParams& prm, const Plan& pl, long long items, int dtype, int block_size,
                   cudaStream_t stream, int num_units = 0) {
-  const bool fuse = prm.k_new != nullptr;
-#define MUX_CASE(T, BS)                                                        \
-  return fuse ? launch_typed<T, BS, MIXED, true>(prm, pl, items, stream, num_units) \
-              : launch_typed<T, BS, MIXED, false>(prm, pl, items, stream, num_units)
+  const int fuse = prm.k_new == nullptr ? 0 : (prm.new_tokens > 1 ? 2 : 1);
+#define MUX_CASE(T, BS)                                                                \
+  return fuse == 0   ? launch_typed<T, BS, MIXED, 0>(prm, pl, items, stream, num_units) \
+         : fuse == 1 ? launch_typed<T, BS, MIXED, 1>(prm, pl, items, stream, num_units) \
+                     : launch_typed<T, BS, MIXED, 2>(prm, pl, items, stream, num_units)
   if (dtype == MUX_DTYPE_F16) {
     if (block_size == 8) MUX_CASE(__half, 8);
     if (block_size == 16) MUX_CASE(__half, 16);
@@ -738,6 +802,7 @@ struct NewRows {  // the decode step's new K/V rows; k == nullptr: plain attenti
   long long k_s0 = 0, k_s1 = 0, v_s0 = 0, v_s1 = 0;
   const void* rope_cache = nullptr;   // optional rotary embedding of q and the new k
   long long rope_max_position = 0;
+  int new_tokens = 1;                 // rows per (sequence, kv head)
 };
 
 static int validate_new_rows(const NewRows& n) {
@@ -746,6 +811,7 @@ static int validate_new_rows(const NewRows& n) {
   if (!aligned16(n.k) || !aligned16(n.v)) return MUX_ERR_MISALIGNED;
   if ((n.k_s0 & 7) || (n.k_s1 & 7) || (n.v_s0 & 7) || (n.v_s1 & 7)) return MUX_ERR_MISALIGNED;
   if (n.rope_cache != nullptr && (!aligned16(n.rope_cache) || n.rope_max_position <= 0)) return MUX_ERR_BAD_SHAPE;
+  if (n.new_tokens < 1 || n.new_tokens > MUX_MAX_FUSED_NEW_TOKENS) return MUX_ERR_BAD_SHAPE;
   return MUX_OK;
 }
 
@@ -799,6 +865,7 @@ static int run_single(const mux_attn_args_t* a, const NewRows& rows, void* works
   prm.vn_s1 = rows.v_s1;
   prm.rope_cache = rows.rope_cache;
   prm.rope_max_position = rows.rope_max_position;
+  prm.new_tokens = rows.new_tokens;
   mux::bind_workspace(prm, pl, workspace);
   if (a->num_units < 0) return MUX_ERR_BAD_SHAPE;
   if (a->num_units > 0) {
@@ -834,6 +901,7 @@ int mux_decode_attention(const mux_decode_args_t* a, void* workspace, size_t wor
   rows.v_s1 = a->v_head_stride;
   rows.rope_cache = a->cos_sin_cache;
   rows.rope_max_position = a->max_position;
+  rows.new_tokens = a->new_tokens > 0 ? a->new_tokens : 1;
   return mux::run_single(&a->attn, rows, workspace, workspace_bytes, cuda_stream);
 }
 
@@ -887,6 +955,7 @@ static int run_mixed(const mux_attn_mixed_args_t* a, const NewRows& rows, void* 
   prm.vn_s0 = rows.v_s0;
   prm.rope_cache = rows.rope_cache;
   prm.rope_max_position = rows.rope_max_position;
+  prm.new_tokens = rows.new_tokens;
   mux::bind_workspace(prm, pl, workspace);
   if (a->num_units < 0) return MUX_ERR_BAD_SHAPE;
   if (a->num_units > 0) {
@@ -918,6 +987,7 @@ int mux_decode_attention_mixed(const mux_decode_mixed_args_t* a, void* workspace
   rows.v_s0 = a->v_row_stride;
   rows.rope_cache = a->cos_sin_cache;
   rows.rope_max_position = a->max_position;
+  rows.new_tokens = a->new_tokens > 0 ? a->new_tokens : 1;
   return mux::run_mixed(&a->attn, rows, workspace, workspace_bytes, cuda_stream);
 }
 

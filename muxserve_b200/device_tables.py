@@ -19,8 +19,19 @@ from ._lib import check, lib
 
 
 class DeviceBlockTables:
-    def __init__(self, num_layers: int, num_kv_heads: int, max_rows: int, max_blocks: int, device="cuda"):
+    """``num_kv_heads`` are the heads THIS process attends over.  On a tensor-parallel rank they are a slice
+    ``[kv_head_start, kv_head_start + num_kv_heads)`` of the model's ``total_kv_heads``: the allocator grants ids for
+    all heads of a logical block (one allocator serves every rank, muxserve/flexstore/manager.py:397-398) and every
+    rank keeps its own heads' columns of the same small grant (``parallel.broadcast_grant`` carries it) instead of
+    receiving the whole rebuilt table (muxserve/flexserver/llm_runtime.py:389-400)."""
+
+    def __init__(self, num_layers: int, num_kv_heads: int, max_rows: int, max_blocks: int, device="cuda",
+                 total_kv_heads: int = None, kv_head_start: int = 0):
         self.L, self.H, self.R, self.max_blocks = num_layers, num_kv_heads, max_rows, max_blocks
+        self.H_total = num_kv_heads if total_kv_heads is None else int(total_kv_heads)
+        self.h0 = int(kv_head_start)
+        if self.h0 < 0 or self.h0 + self.H > self.H_total:
+            raise ValueError("the local kv heads must be a slice of the model's")
         self.tables = torch.zeros((num_layers, max_rows, num_kv_heads, max_blocks), dtype=torch.int32, device=device)
         self.row_of: Dict[int, int] = {}
         self.blocks_of: Dict[int, int] = {}          # physical blocks already in the table, per request
@@ -55,7 +66,7 @@ class DeviceBlockTables:
         granted logical block is L*H ids in [layer][head] order."""
         req = np.asarray(batch_block_request, dtype=np.int64).reshape(-1, 3)
         info = np.asarray(block_info, dtype=np.int32)
-        keep, off, LH = int(info[0]), 1, self.L * self.H
+        keep, off, LH = int(info[0]), 1, self.L * self.H_total
         for i in range(min(keep, len(req))):
             rid, n = int(req[i, 0]), int(req[i, 1])
             if n <= 0:
@@ -67,7 +78,8 @@ class DeviceBlockTables:
             for j in range(n):
                 self._rows.append(row)
                 self._blks.append(first + j)
-            self._ids.append(info[off:off + n * LH].reshape(n, LH))
+            ids = info[off:off + n * LH].reshape(n, self.L, self.H_total)[:, :, self.h0:self.h0 + self.H]
+            self._ids.append(np.ascontiguousarray(ids).reshape(n, self.L * self.H))
             off += n * LH
             self.blocks_of[rid] = first + n
         for i in range(max(keep, 0), len(req)):           # preempted by the allocator

@@ -18,7 +18,7 @@ from . import _lib
 from ._lib import AttnArgs, AttnMixedArgs, CacheWriteArgs, check, lib
 
 HEAD_SIZE = 128
-MAX_FUSED_NEW_TOKENS = 1   # new tokens per sequence that decode_attention appends in its own launch
+MAX_FUSED_NEW_TOKENS = 16  # new tokens per sequence that decode_attention appends in its own launch
 
 _DTYPES = {torch.float16: _lib.MUX_DTYPE_F16, torch.bfloat16: _lib.MUX_DTYPE_BF16}
 _workspaces = {}
@@ -225,13 +225,16 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, key_cache: torch.Tensor,
                              "block list ([S, H, max_blocks] block_tables)")
         Tk, Hk, k_ss, k_hs = _rows(k, "k")
         Tv, Hv, v_ss, v_hs = _rows(v, "v")
-        if (Tk, Hk) != (S, H) or (Tv, Hv) != (S, H):
-            raise ValueError(f"k and v must hold one new row per (sequence, kv head): [{S}, {H}, {HEAD_SIZE}]")
+        NT = Tk // S if S > 0 and Tk % S == 0 else 0
+        if NT < 1 or NT > MAX_FUSED_NEW_TOKENS or (Tk, Hk) != (S * NT, H) or (Tv, Hv) != (Tk, H):
+            raise ValueError(f"k and v must hold 1..{MAX_FUSED_NEW_TOKENS} new rows per (sequence, kv head), token-major "
+                             f"within a sequence: [{S} * new_tokens, {H}, {HEAD_SIZE}]")
         if k.dtype != key_cache.dtype or v.dtype != key_cache.dtype:
             raise TypeError("k/v dtype differs from the pool dtype")
         rope_ptr, rope_len = _rope_cache(_rope, q)
         dargs = _lib.DecodeArgs(attn=args, k=k.data_ptr(), v=v.data_ptr(), k_seq_stride=k_ss, k_head_stride=k_hs,
-                                v_seq_stride=v_ss, v_head_stride=v_hs, cos_sin_cache=rope_ptr, max_position=rope_len)
+                                v_seq_stride=v_ss, v_head_stride=v_hs, cos_sin_cache=rope_ptr, max_position=rope_len,
+                                new_tokens=NT, reserved=0)
         check(L.mux_decode_attention(C.byref(dargs), ws.data_ptr() if ws is not None else None,
                                      ws.numel() if ws is not None else 0, _stream()), "decode_attention")
     global launch_count
@@ -361,6 +364,8 @@ def decode_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: tor
     appended at position ``context_lens[s] - 1`` of block list ``block_tables[s, h]`` — the slot
     the reference's ``slot_mapping`` names for a decode step (csrc/batch_scheduler.h:58-67) — and
     attention runs over all ``context_lens[s]`` tokens.  Results equal the two separate ops bit for bit.
+    ``k``, ``v`` may also hold n <= 16 new rows per sequence, [S*n, H(*128)] token-major within a sequence: they go
+    to positions ``context_lens[s] - n .. context_lens[s] - 1`` (the context length counts them all).
     With ``cos_sin_cache`` the query and the new key are first rotated at position ``context_lens[s] - 1``
     (neither ``q`` nor ``k`` is modified), as ``rotary_embedding`` would.
     """
@@ -433,13 +438,15 @@ def paged_attention_mixed(out: torch.Tensor, q: torch.Tensor, key_cache: torch.T
               "paged_attention_mixed")
     else:
         _require_cuda(new_k=new_k, new_v=new_v)
+        NT = new_k.shape[0] // n if n > 0 and new_k.dim() == 2 and new_k.shape[0] % n == 0 else 0
         for name, t in (("new_k", new_k), ("new_v", new_v)):
-            if t.dim() != 2 or tuple(t.shape) != (n, HEAD_SIZE) or t.stride(1) != 1 or t.dtype != q.dtype:
-                raise ValueError(f"{name} must be [{n}, {HEAD_SIZE}] of the pool dtype with a dense last dim")
+            if (NT < 1 or NT > MAX_FUSED_NEW_TOKENS or t.dim() != 2 or tuple(t.shape) != (n * NT, HEAD_SIZE)
+                    or t.stride(1) != 1 or t.dtype != q.dtype):
+                raise ValueError(f"{name} must be [{n} * new_tokens, {HEAD_SIZE}] of the pool dtype with a dense last dim")
         rope_ptr, rope_len = _rope_cache(cos_sin_cache, q)
         dargs = _lib.DecodeMixedArgs(attn=args, k=new_k.data_ptr(), v=new_v.data_ptr(),
                                      k_row_stride=new_k.stride(0), v_row_stride=new_v.stride(0),
-                                     cos_sin_cache=rope_ptr, max_position=rope_len)
+                                     cos_sin_cache=rope_ptr, max_position=rope_len, new_tokens=NT, reserved=0)
         check(L.mux_decode_attention_mixed(C.byref(dargs), ws.data_ptr() if ws is not None else None,
                                            ws.numel() if ws is not None else 0, _stream()),
               "decode_attention_mixed")

@@ -58,6 +58,33 @@ def shard_index_tensors(shard: HeadShard, block_tables: torch.Tensor, slot_mappi
     return block_tables[:, :, sl, :], slot_mapping[:, :, sl]
 
 
+def broadcast_grant(batch_block_request, block_info, src: int = 0, group: Optional[dist.ProcessGroup] = None,
+                    device="cpu"):
+    """Carries one step's allocator answer — the rows ``[request id, blocks, has_blocks]`` and ``[preempt_idx,
+    ids...]``, a few KB — from the rank that runs the scheduler to every rank of the TP group.  The reference
+    broadcasts the rebuilt ``slot_mapping`` / ``context_lens`` / ``block_tables`` tensors instead
+    (muxserve/flexserver/llm_runtime.py:389-400: 33 MB per step for 64 LLaMA-7B sequences); here every rank applies
+    the grant to its own ``DeviceBlockTables`` (its heads' columns).  ``device``: where the group's backend wants
+    its tensors ("cpu" for gloo, the rank's GPU for nccl).  Returns the two int32 numpy arrays on every rank."""
+    import numpy as np
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return np.asarray(batch_block_request, dtype=np.int32).reshape(-1), np.asarray(block_info, dtype=np.int32).reshape(-1)
+    mine = dist.get_rank(group) == src
+    head = torch.zeros(2, dtype=torch.int64, device=device)
+    if mine:
+        req = torch.as_tensor(np.asarray(batch_block_request, dtype=np.int32).reshape(-1))
+        info = torch.as_tensor(np.asarray(block_info, dtype=np.int32).reshape(-1))
+        head = torch.tensor([req.numel(), info.numel()], dtype=torch.int64, device=device)
+    dist.broadcast(head, src=src, group=group)
+    n_req, n_info = (int(x) for x in head.tolist())
+    payload = torch.empty(n_req + n_info, dtype=torch.int32, device=device)
+    if mine:
+        payload.copy_(torch.cat([req, info]))
+    dist.broadcast(payload, src=src, group=group)
+    host = payload.cpu().numpy()
+    return host[:n_req].copy(), host[n_req:].copy()
+
+
 def all_reduce_output(partial: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Sum of the ranks' partial [tokens, hidden] outputs, in place (the TP all-reduce after o_proj)."""
     if dist.is_initialized() and dist.get_world_size(group) > 1:

@@ -72,3 +72,73 @@ def test_tp2_gloo_allreduce_matches_single_rank():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == [(0, True, True, 2.0), (1, True, True, 2.0)]
+
+
+def _grant_worker(rank, world, port, q_out):
+    """Rank 0 runs the allocator and the step builder for ALL heads; every rank receives the few-KB grant and keeps
+    its own heads' columns in its persistent table, which must equal its slice of the rebuilt full table."""
+    import numpy as np
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from muxserve_b200.batch_scheduler import BatchScheduler
+        from muxserve_b200.device_tables import DeviceBlockTables
+        from muxserve_b200.memory_manager import KVStorage
+        L, H, B, max_seq = 3, 4, 16, 128
+        shard = parallel.shard_heads(H, H, world, rank)
+        dbt = DeviceBlockTables(L, shard.kv_count, max_rows=4, max_blocks=max_seq // B, device="cpu",
+                                total_kv_heads=H, kv_head_start=shard.kv_start)
+        ids = [7, 8, 9]
+        if rank == 0:
+            kv, sched = KVStorage(1024), BatchScheduler(L, H, max_seq, B)
+            for r, n in zip(ids, [5, 16, 31]):
+                sched.add_request(np.arange(n, dtype=np.int32), r, 64)
+        ok, sent = True, 0
+        for step in range(24):
+            req = info = None
+            if rank == 0:
+                req = sched.try_batch(ids, [] if step == 0 else [step] * len(ids))
+                info = kv.allocate_batch(req[:-1], L, H) if req[-1] > 0 else np.array([len(ids)], dtype=np.int32)
+                req = req[:-1]
+            req, info = parallel.broadcast_grant(req, info, src=0)
+            sent += req.nbytes + info.nbytes
+            dbt.stage_grant(req, info)
+            for row, blk, block_ids in zip(dbt._rows, dbt._blks, np.concatenate(dbt._ids) if dbt._ids else []):
+                dbt.tables[:, row, :, blk] = torch.from_numpy(block_ids.reshape(L, shard.kv_count))   # what flush scatters
+            dbt._rows, dbt._blks, dbt._ids = [], [], []
+            full = None
+            if rank == 0:
+                ntok, nctx, maxctx, maxblk = sched.get_batch_info(req, info)[:4]
+                if step > 0:
+                    S = len(ids)
+                    tok, pos, ctx = torch.empty(8, dtype=torch.int32), torch.empty(8, dtype=torch.int32), torch.empty(S, dtype=torch.int32)
+                    full = torch.zeros((L, S, H, max_seq // B), dtype=torch.int32)
+                    view = torch.empty((L, S, H, maxblk), dtype=torch.int32)
+                    sched.get_batch_decode_layered(req, info, tok, pos, ctx, view, torch.empty((S, L, H), dtype=torch.int64))
+                    full[..., :maxblk] = view
+            box = [full]
+            dist.broadcast_object_list(box, src=0)                  # the check's reference only
+            if box[0] is not None:
+                rows = torch.tensor([dbt.row_of[r] for r in ids])
+                mine = dbt.tables[:, rows]
+                want = box[0][:, :, shard.kv_start:shard.kv_start + shard.kv_count]
+                nb = [dbt.blocks_of[r] for r in ids]
+                for s, n in enumerate(nb):
+                    ok = ok and torch.equal(mine[:, s, :, :n], want[:, s, :, :n])
+        q_out.put((rank, bool(ok), sent < 24 * 3 * L * H * (max_seq // B) * 4))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_grant_broadcast_keeps_each_ranks_heads():
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_grant_worker, args=(r, 2, port, q_out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q_out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results == [(0, True, True), (1, True, True)]
