@@ -421,7 +421,8 @@ int mux_tp_buffer_destroy(void* ptr);                   /* what mux_tp_buffer_cr
 int mux_tp_buffer_export(const void* ptr, unsigned char handle[MUX_TP_IPC_HANDLE_BYTES]);
 int mux_tp_buffer_import(const unsigned char handle[MUX_TP_IPC_HANDLE_BYTES], void** ptr);
 int mux_tp_buffer_release(void* ptr);                   /* what mux_tp_buffer_import returned */
-/* out = sum over ranks of in; count elements (multiple of 8) of dtype.  num_ctas 0 = heuristic (<= 64).
+/* out = sum over ranks of in; count elements (multiple of 8) of dtype.  Every launch has 32 CTAs; num_ctas says how
+ * many of them move data (0 = heuristic), the others only exchange flags.
  * MUX_ERR_TOO_LARGE when the message does not fit the exchange buffers. */
 int mux_tp_allreduce(const mux_tp_comm_t* comm, const void* in, void* out, int64_t count, int32_t dtype,
                      int32_t algo, int32_t num_ctas, void* cuda_stream);

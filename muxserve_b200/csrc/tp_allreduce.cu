@@ -16,11 +16,12 @@
 //
 // Synchronisation is per CTA index: CTA b of every rank works on chunk b and only ever
 // waits for CTA b of the other ranks, so no grid-wide barrier is needed and the CTAs of
-// a launch need not be resident together.  Flags carry the launch's epoch (a counter
-// kept in the exchange buffer, advanced by the last CTA of each launch), data slots
-// alternate with the epoch's parity: a rank can start epoch e + 2, the next user of a
-// slot, only after every peer raised its flag of epoch e + 1, i.e. after every peer's
-// kernel of epoch e has ended.  Every wait is bounded; when one runs out the kernel sets
+// a launch need not be resident together.  Every launch has the same number of CTAs
+// (those beyond the ones that move data only exchange flags), so a CTA's own call
+// counter — kept in the exchange buffer, no atomics — is the launch's epoch on every
+// rank.  Flags carry the epoch, data slots alternate with its parity: a rank can start
+// epoch e + 2, the next user of a slot, only after every peer raised its flag of epoch
+// e + 1, i.e. after every peer's kernel of epoch e has ended.  Every wait is bounded; when one runs out the kernel sets
 // MUX_DEV_WAIT_TIMEOUT and goes on to its end (results are then garbage, nothing hangs).
 // No multimem, no TMA, no cluster multicast: plain ld / st on peer pointers.
 #include <cooperative_groups.h>
@@ -32,18 +33,18 @@
 #include <cstring>
 
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace mux {
 
 constexpr int kArMaxWorld = MUX_TP_MAX_WORLD;
 constexpr int kArMaxCtas = 64;
+constexpr int kArCtas = 32;  // CTAs of every launch
 constexpr int kArThreads = 512;
 constexpr unsigned kArWaitLimit = 1u << 23;  // polls of ~0.4 us: a few seconds
 
 struct ArCtrl {
-  unsigned epoch;                            // launches completed on this rank
-  unsigned arrived;                          // CTAs of the running launch that have finished
-  unsigned pad[30];
+  unsigned epoch[kArMaxCtas];                // per CTA: launches completed on this rank
   unsigned ready[kArMaxWorld][kArMaxCtas];   // [source rank][cta]: source's chunk is published (epoch value)
   unsigned done[kArMaxWorld][kArMaxCtas];    // two-shot: source's reduced slice has been pushed
 };
@@ -136,7 +137,11 @@ template <typename T>
 __device__ void allreduce_body(const ArParams& p, int rank, int cta) {
   const int tid = threadIdx.x, world = p.world;
   ArCtrl* my = reinterpret_cast<ArCtrl*>(p.buf[rank]);
-  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&my->epoch) + 1u;
+  // launched with programmatic dependent launch: the CTA may be resident before the kernel ahead has ended,
+  // and that kernel may be this rank's previous all-reduce (which stores the counter read next) or the producer of `in`
+  griddep_wait();
+  griddep_launch_dependents();
+  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&my->epoch[cta]) + 1u;
   const size_t slot_off = kArCtrlBytes + (size_t)(epoch & 1u) * (size_t)p.slot_bytes;
   const size_t msg_bytes = (size_t)p.nvec * 16;
   const uint4* in = static_cast<const uint4*>(p.in[rank]);
@@ -151,8 +156,7 @@ __device__ void allreduce_body(const ArParams& p, int rank, int cta) {
       for (int q = 0; q < world; ++q)
         *reinterpret_cast<uint4*>(p.buf[q] + slot_off + (size_t)rank * msg_bytes + (size_t)v * 16) = x;
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // the releasing flag stores below are cumulative: they order every thread's pushes before the flag
     if (tid < world) st_flag(&reinterpret_cast<ArCtrl*>(p.buf[tid])->ready[rank][cta], epoch);
     wait_flags(&my->ready[0][cta], world, epoch, p.status);
     const unsigned char* mine = p.buf[rank] + slot_off;
@@ -171,8 +175,7 @@ __device__ void allreduce_body(const ArParams& p, int rank, int cta) {
       for (long long v = lo + tid; v < hi; v += kArThreads)
         *reinterpret_cast<uint4*>(p.buf[rank] + a_off + (size_t)v * 16) = in[v];
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // the releasing flag stores below are cumulative: they order every thread's pushes before the flag
     if (tid < world) st_flag(&reinterpret_cast<ArCtrl*>(p.buf[tid])->ready[rank][cta], epoch);
     wait_flags(&my->ready[0][cta], world, epoch, p.status);
     {
@@ -190,8 +193,7 @@ __device__ void allreduce_body(const ArParams& p, int rank, int cta) {
         for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(p.buf[q] + b_off + (size_t)v * 16) = r;
       }
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // the releasing flag stores below are cumulative: they order every thread's pushes before the flag
     if (tid < world) st_flag(&reinterpret_cast<ArCtrl*>(p.buf[tid])->done[rank][cta], epoch);
     wait_flags(&my->done[0][cta], world, epoch, p.status);
     for (int s = 0; s < world; ++s) {
@@ -200,16 +202,8 @@ __device__ void allreduce_body(const ArParams& p, int rank, int cta) {
     }
   }
 
-  // The last CTA of the launch to finish advances the epoch for the next launch.
   __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    if (atomicAdd(&my->arrived, 1u) == (unsigned)p.ncta - 1u) {
-      my->arrived = 0u;
-      __threadfence();
-      *reinterpret_cast<volatile unsigned*>(&my->epoch) = epoch;
-    }
-  }
+  if (tid == 0) my->epoch[cta] = epoch;  // this CTA's next launch (after this kernel has ended) is epoch + 1
 }
 
 template <typename T>
@@ -230,11 +224,12 @@ static int pick_algo(int algo, int world, size_t bytes) {
   return (size_t)(world - 1) * bytes <= (size_t)MUX_TP_ONE_SHOT_MAX_PUSH_BYTES ? MUX_TP_ONE_SHOT : MUX_TP_TWO_SHOT;
 }
 
+// How many of the launch's kArCtas CTAs move data (the others only exchange flags).
 static int pick_ctas(int num_ctas, int algo, int world, long long nvec) {
-  if (num_ctas > 0) return std::min(num_ctas, kArMaxCtas);
+  if (num_ctas > 0) return std::min(num_ctas, kArCtas);
   // enough CTAs to keep the links busy, at least ~4 KiB of the message per CTA
   const long long share = algo == MUX_TP_ONE_SHOT ? nvec : (nvec + world - 1) / world;
-  return (int)std::max<long long>(1, std::min<long long>(kArMaxCtas, share / 256));
+  return (int)std::max<long long>(1, std::min<long long>(kArCtas, share / 256));
 }
 
 static int fill_params(ArParams& prm, int world, void* const* buffers, long long buffer_bytes, long long count,
@@ -359,11 +354,17 @@ int mux_tp_allreduce(const mux_tp_comm_t* comm, const void* in, void* out, int64
   prm.status = mux::device_status_ptr();
   if (prm.status == nullptr) return MUX_ERR_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-  if (dtype == MUX_DTYPE_F16)
-    mux::tp_allreduce_kernel<__half><<<prm.ncta, mux::kArThreads, 0, s>>>(prm);
-  else
-    mux::tp_allreduce_kernel<__nv_bfloat16><<<prm.ncta, mux::kArThreads, 0, s>>>(prm);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(mux::kArCtas);
+  cfg.blockDim = dim3(mux::kArThreads);
+  cfg.stream = s;
+  cfg.attrs = pdl;
+  cfg.numAttrs = 1;
+  cudaError_t e = dtype == MUX_DTYPE_F16 ? cudaLaunchKernelEx(&cfg, mux::tp_allreduce_kernel<__half>, prm)
+                                         : cudaLaunchKernelEx(&cfg, mux::tp_allreduce_kernel<__nv_bfloat16>, prm);
   return e == cudaSuccess ? MUX_OK : mux::record_cuda_error(e);
 }
 
@@ -389,15 +390,7 @@ int mux_tp_allreduce_emulated(int32_t world, void* const* buffers, int64_t buffe
   void* kargs[] = {&prm};
   const void* fn = dtype == MUX_DTYPE_F16 ? (const void*)mux::tp_allreduce_emulated_kernel<__half>
                                           : (const void*)mux::tp_allreduce_emulated_kernel<__nv_bfloat16>;
-  if (num_ctas == 0) {  // the heuristic count is per rank; here all ranks share one GPU
-    int dev = 0, sms = 0, per_sm = 0;
-    cudaError_t q = cudaGetDevice(&dev);
-    if (q == cudaSuccess) q = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (q == cudaSuccess) q = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, mux::kArThreads, 0);
-    if (q != cudaSuccess) return mux::record_cuda_error(q);
-    prm.ncta = std::max(1, std::min(prm.ncta, sms * per_sm / world));
-  }
-  const dim3 grid((unsigned)prm.ncta, (unsigned)world);
+  const dim3 grid((unsigned)mux::kArCtas, (unsigned)world);
   cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, dim3(mux::kArThreads), kargs, 0,
                                               static_cast<cudaStream_t>(cuda_stream));
   return e == cudaSuccess ? MUX_OK : mux::record_cuda_error(e);
