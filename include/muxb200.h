@@ -403,6 +403,7 @@ int mux_block_table_append(int32_t* tables, int64_t layer_stride, int64_t row_st
  * one stream per rank.  in == out is allowed.  Ranks of one process may pass plain device pointers.
  * ---------------------------------------------------------------------- */
 #define MUX_TP_MAX_WORLD 8
+#define MUX_TP_CTRL_BYTES 32768                /* flags and call counters at the start of every exchange buffer */
 #define MUX_TP_AUTO 0
 #define MUX_TP_ONE_SHOT 1                      /* each rank pushes its message to all, sums locally */
 #define MUX_TP_TWO_SHOT 2                      /* reduce-scatter by peer loads + all-gather by peer stores */
@@ -426,6 +427,37 @@ int mux_tp_buffer_release(void* ptr);                   /* what mux_tp_buffer_im
  * MUX_ERR_TOO_LARGE when the message does not fit the exchange buffers. */
 int mux_tp_allreduce(const mux_tp_comm_t* comm, const void* in, void* out, int64_t count, int32_t dtype,
                      int32_t algo, int32_t num_ctas, void* cuda_stream);
+/* ------------------------------------------------------------------------
+ * o_proj GEMM fused with the all-reduce of its result: what the row-parallel output projection of the
+ * reference's attention layer does in two steps (muxserve/flexserver/models/llama.py:131-137,162: the fork's
+ * ParallelLinear.row, then the NCCL all-reduce over the TP group), in ONE kernel per rank:
+ *   out[t, n] = sum over ranks r of round16( sum_k a_r[t, k] * w_r[n, k] )      (fp32 inside, rank order)
+ * a_r = the rank's attention output [m, k] (k = local q heads * 128), w_r = the rank's slice [n, k] of the
+ * o_proj weight (nn.Linear's [out_features, in_features] layout, sliced along in_features), out [m, n] on every
+ * rank.  The GEMM runs on tcgen05 tensor cores (TMA-staged operands, accumulators in tensor memory); every
+ * 128 x 64 output tile is exchanged as soon as it is finished: pushed to the tile's owner rank, summed there,
+ * pushed back to all (plain peer stores, bounded waits).  m <= 128; n a multiple of 64, <= MUX_TP_OPROJ_MAX_COLS;
+ * k a multiple of 64; strides in elements, multiples of 8.  comm == NULL (or world 1): the GEMM alone.
+ * A communicator used for this call must be used ONLY for it, always with the same n, by all ranks in the same
+ * order (its exchange buffer: mux_tp_allreduce_buffer_size(world, m_max * n * 2)).
+ * ---------------------------------------------------------------------- */
+#define MUX_TP_OPROJ_MAX_COLS 16384
+typedef struct {
+  const void* a;
+  int64_t a_row_stride;
+  const void* w;
+  int64_t w_row_stride;
+  void* out;
+  int64_t out_row_stride;
+  int32_t m, n, k;
+  int32_t dtype;
+} mux_oproj_args_t;
+int mux_tp_oproj_allreduce(const mux_tp_comm_t* comm, const mux_oproj_args_t* args, void* cuda_stream);
+/* All ranks of a world as one cooperative launch on ONE GPU (tests of the protocol): args[r] are rank r's
+ * operands, maps_scratch is 2 * world * 128 bytes of device memory (64-byte aligned) for the ranks' copy descriptors. */
+int mux_tp_oproj_allreduce_emulated(int32_t world, void* const* buffers, int64_t buffer_bytes,
+                                    const mux_oproj_args_t* args, void* maps_scratch, void* cuda_stream);
+
 /* The same device code for a whole world on ONE GPU: rank r uses buffers[r], ins[r], outs[r]; all ranks'
  * CTAs form one cooperative launch (they wait on one another).  For tests of the protocol without
  * several GPUs; fails with MUX_ERR_CUDA when the grid cannot be resident at once. */

@@ -26,7 +26,7 @@ MUX_ATTN_EARLY_KV = 1
 
 MUX_TP_AUTO, MUX_TP_ONE_SHOT, MUX_TP_TWO_SHOT = 0, 1, 2
 
-ABI_VERSION = 14
+ABI_VERSION = 15
 
 
 class CacheWriteArgs(C.Structure):
@@ -132,6 +132,12 @@ class TpComm(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("buffers", C.c_void_p * 8), ("buffer_bytes", C.c_int64)]
 
 
+class OprojArgs(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("a_row_stride", C.c_int64), ("w", C.c_void_p), ("w_row_stride", C.c_int64),
+                ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("dtype", C.c_int32)]
+
+
 class MixedModel(C.Structure):
     _fields_ = [("scheduler", C.c_void_p), ("request_ids", C.POINTER(C.c_int32)), ("num_requests", C.c_int32),
                 ("num_q_heads", C.c_int32), ("scale", C.c_float)]
@@ -173,6 +179,9 @@ SIGNATURES = {
     "mux_tp_allreduce_emulated": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p), C.c_int64, C.POINTER(C.c_void_p),
                                             C.POINTER(C.c_void_p), C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_void_p]),
+    "mux_tp_oproj_allreduce": (C.c_int, [C.POINTER(TpComm), C.POINTER(OprojArgs), C.c_void_p]),
+    "mux_tp_oproj_allreduce_emulated": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p), C.c_int64, C.POINTER(OprojArgs),
+                                                  C.c_void_p, C.c_void_p]),
     "mux_selftest_wait_timeout": (C.c_int, [C.c_void_p]),
     "mux_device_status": (C.c_int, [C.c_void_p]),
     "mux_kv_storage_create": (C.c_void_p, [C.c_int32]),

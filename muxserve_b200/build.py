@@ -20,7 +20,7 @@ LIB_PATH = PKG_DIR / "libmuxb200.so"
 BUILD_DIR = PKG_DIR / "build"
 
 CUDA_SOURCES = ["status.cu", "cache_write.cu", "rotary.cu", "block_table.cu", "paged_attention.cu",
-                "prefill_attention.cu", "tp_allreduce.cu"]
+                "prefill_attention.cu", "tp_allreduce.cu", "oproj_allreduce.cu"]
 HOST_SOURCES = ["host/kv_storage.cpp", "host/batch_scheduler.cpp"]
 HEADERS = ["ptx.cuh", "internal.h", "attn_common.cuh", "rope.cuh", "../../include/muxb200.h"]
 

@@ -48,8 +48,8 @@ struct ArCtrl {
   unsigned ready[kArMaxWorld][kArMaxCtas];   // [source rank][cta]: source's chunk is published (epoch value)
   unsigned done[kArMaxWorld][kArMaxCtas];    // two-shot: source's reduced slice has been pushed
 };
-constexpr size_t kArCtrlBytes = 8192;
-static_assert(sizeof(ArCtrl) <= kArCtrlBytes, "control block");
+constexpr size_t kArCtrlBytes = MUX_TP_CTRL_BYTES;  // this op's block is the first 8 KiB; the fused o_proj's follows
+static_assert(sizeof(ArCtrl) <= 8192, "control block");
 
 struct ArParams {
   unsigned char* buf[kArMaxWorld];   // exchange buffers of all ranks as mapped in this process

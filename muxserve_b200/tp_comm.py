@@ -58,7 +58,7 @@ class TPAllReduce:
                 check(L.mux_tp_buffer_import(raw, C.byref(p)), "tp_buffer_import")
                 self._imported.append(p)
                 ptrs.append(p.value)
-        self.slot_bytes = (nbytes - 8192) // 2      # what one message's exchange area may take (one-shot: world x message)
+        self.slot_bytes = (nbytes - 32768) // 2     # what one message's exchange area may take (one-shot: world x message)
         self.comm = _lib.TpComm(world=self.world, rank=self.rank, buffer_bytes=nbytes)
         for r, p in enumerate(ptrs):
             self.comm.buffers[r] = p
@@ -107,4 +107,65 @@ def all_reduce_emulated(inputs: List[torch.Tensor], max_message_bytes: Optional[
     check(lib().mux_tp_allreduce_emulated(world, arr(buffers), buffers[0].numel(), arr(inputs), arr(outs),
                                           inputs[0].numel(), _DTYPES[inputs[0].dtype], algo, num_ctas,
                                           torch.cuda.current_stream().cuda_stream), "tp_allreduce_emulated")
+    return outs, buffers
+
+
+def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> "_lib.OprojArgs":
+    if a.dim() != 2 or w.dim() != 2 or out.dim() != 2:
+        raise ValueError("a [m, k], w [n, k] and out [m, n] must be 2-D")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n):
+        raise ValueError(f"shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.dtype not in _DTYPES or w.dtype != a.dtype or out.dtype != a.dtype:
+        raise TypeError("a, w and out must be float16 or bfloat16 tensors of one dtype")
+    for name, t in (("a", a), ("w", w), ("out", out)):
+        if not t.is_cuda or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a CUDA tensor with a dense last dimension")
+    return _lib.OprojArgs(a=a.data_ptr(), a_row_stride=a.stride(0), w=w.data_ptr(), w_row_stride=w.stride(0),
+                          out=out.data_ptr(), out_row_stride=out.stride(0), m=m, n=n, k=k, dtype=_DTYPES[a.dtype])
+
+
+def oproj(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = a @ w.T`` on the tcgen05 GEMM of the fused kernel, without any exchange (one rank)."""
+    args = _oproj_args(a, w, out)
+    check(lib().mux_tp_oproj_allreduce(None, C.byref(args), torch.cuda.current_stream().cuda_stream), "tp_oproj")
+    return out
+
+
+class TPOProj(TPAllReduce):
+    """The row-parallel output projection of a TP rank fused with the all-reduce of its result
+    (muxserve/flexserver/models/llama.py:131-137,162).  One instance per hidden size: its communicator is used for
+    nothing else, and every rank calls ``forward`` in the same order."""
+
+    def __init__(self, max_tokens: int, hidden: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        super().__init__(max_tokens * hidden * 2, device, group)
+        self.hidden = hidden
+
+    def forward(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``out[t, n] = sum over ranks of round(a_rank[t, :] @ w_rank[n, :])``; ``a`` [tokens, local q heads * 128],
+        ``w`` [hidden, local q heads * 128] (this rank's columns of the o_proj weight), ``out`` [tokens, hidden]."""
+        if w.shape[0] != self.hidden:
+            raise ValueError(f"this communicator was made for hidden size {self.hidden}")
+        args = _oproj_args(a, w, out)
+        check(lib().mux_tp_oproj_allreduce(C.byref(self.comm), C.byref(args), torch.cuda.current_stream().cuda_stream),
+              "tp_oproj_allreduce")
+        return out
+
+
+def oproj_allreduce_emulated(a_list: List[torch.Tensor], w_list: List[torch.Tensor], buffers=None):
+    """The fused kernel for ``len(a_list)`` ranks on ONE GPU (one cooperative launch); returns (outs, buffers)."""
+    world = len(a_list)
+    m, n = a_list[0].shape[0], w_list[0].shape[0]
+    dev = a_list[0].device
+    nbytes = buffer_size(world, m * n * 2)
+    if buffers is None:
+        buffers = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+    outs = [torch.empty((m, n), dtype=a_list[0].dtype, device=dev) for _ in range(world)]
+    args = (_lib.OprojArgs * world)(*[_oproj_args(a, w, o) for a, w, o in zip(a_list, w_list, outs)])
+    bufs = (C.c_void_p * world)(*[b.data_ptr() for b in buffers])
+    scratch = torch.empty(2 * world * 128, dtype=torch.uint8, device=dev)
+    check(lib().mux_tp_oproj_allreduce_emulated(world, bufs, nbytes, args, scratch.data_ptr(),
+                                                torch.cuda.current_stream().cuda_stream), "tp_oproj_allreduce_emulated")
+    torch.cuda.synchronize()          # `scratch` holds the launch's copy descriptors
     return outs, buffers
