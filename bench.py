@@ -1144,6 +1144,65 @@ def allreduce_sweep(env: Env, comm):
     return rows
 
 
+def oproj_leg(env: Env, comm, name: str):
+    """The step after attention on a TP rank: o_proj (row-parallel GEMM of the rank's heads' output with its weight
+    slice) + the all-reduce of the [tokens, hidden] result, as ONE fused kernel per layer (tcgen05 GEMM whose epilogue
+    exchanges the tiles), against the library's GEMM followed by its all-reduce and against torch.matmul (cuBLAS)
+    followed by NCCL.  Weights of 16 layers are cycled (more than L2 holds); numerics: the fused result equals the
+    rank-order sum of the ranks' rounded partial products exactly."""
+    from muxserve_b200 import tp_comm
+    dist, dev, world = env.dist, env.dev, env.world
+    w = WORKLOADS[name]
+    dt = DTYPES[w["dtype"]]
+    hidden, L = w["Hq"] * 128, w["L"]
+    k = hidden // world
+    m = min(w["S"], 128)
+    Lw = min(L, 16)
+    gen = torch.Generator(device=dev).manual_seed(env.args.seed + env.rank)
+    a = torch.randn((m, k), generator=gen, device=dev).to(dt)
+    wt = (torch.randn((Lw, hidden, k), generator=gen, device=dev) / hidden ** 0.5).to(dt)
+    out = torch.empty((m, hidden), dtype=dt, device=dev)
+    tmp = torch.empty_like(out)
+    op = tp_comm.TPOProj(m, hidden, dev)
+    # numerics
+    op.forward(a, wt[0], out)
+    part = torch.empty_like(out)
+    tp_comm.oproj(a, wt[0], part)
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    acc = torch.zeros_like(part, dtype=torch.float32)
+    for p_ in parts:
+        acc += p_.float()
+    torch.cuda.synchronize()
+    exact = bool(torch.equal(out, acc.to(dt)))
+    ref = a.float() @ wt[0].float().T
+    gemm_err = float((part.float() - ref).abs().max())
+    res = {"m": m, "n": hidden, "k_local": k, "fused_equals_rank_order_sum_of_rounded_partials": exact,
+           "gemm_max_abs_err_vs_fp32": gemm_err}
+
+    def timed(fn, label):
+        run, _, _ = env.capture(lambda: [fn(l % Lw) for l in range(L)], label)
+        ms, _ = env.timed(run, env.args.steps, 3, target_s=0.3)
+        return ms * 1e3 / L
+
+    res["fused_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out), "fused o_proj")
+    res["gemm_then_allreduce_us_per_layer"] = timed(lambda i: (tp_comm.oproj(a, wt[i], tmp), comm.all_reduce(tmp, out)),
+                                                    "o_proj then all-reduce")
+    res["cublas_then_nccl_us_per_layer"] = timed(lambda i: (torch.matmul(a, wt[i].T, out=tmp), dist.all_reduce(tmp)),
+                                                 "cuBLAS then NCCL")
+    res["gemm_alone_us_per_layer"] = timed(lambda i: tp_comm.oproj(a, wt[i], tmp), "o_proj alone")
+    flops, wbytes = 2.0 * m * hidden * k, hidden * k * 2
+    link = 2.0 * (world - 1) / world * m * hidden * 2
+    peak_t, _ = tensor_peak()
+    peak_h, _ = hbm_peak()
+    target = max(flops / (peak_t * 1e12), wbytes / (peak_h * 1e9), link / 770e9) * 1e6
+    res["roofline"] = {"bound": "max(tensor, hbm weight read, nvlink)", "target_us": target,
+                       "achieved_over_target": target / res["fused_us_per_layer"],
+                       "flops": flops, "weight_bytes": wbytes, "nvlink_bytes_per_rank": link,
+                       "nvlink_peak": "770 GB/s per direction per GPU (measured peer copy on this pool)"}
+    return res
+
+
 # ----------------------------------------------------------------------------- orchestration
 def base_line(env, args, res, name, desc, dtype, scaling, placement, extra_cfg=None):
     cfg = {"workload": f"{name}: {desc}", "block_size": BLOCK, "seed": args.seed,
@@ -1284,6 +1343,8 @@ def run_native_tp(env: Env):
     if not args.no_tp_extras:
         log("all-reduce sweep")
         tp["allreduce_sweep"] = allreduce_sweep(env, comm)
+        log("fused o_proj")
+        tp["oproj_fused"] = {n: oproj_leg(env, comm, n) for n in (name, "c2") if WORKLOADS[n]["Hq"] % world == 0}
         others = {}
         for n in ("c4", "c5", "c2"):          # bf16 workloads first: the pool is re-filled only once
             if n == name or WORKLOADS[n]["H"] % world != 0:

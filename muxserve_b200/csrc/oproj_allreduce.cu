@@ -385,15 +385,16 @@ static int validate(const mux_oproj_args_t* a) {
   return MUX_OK;
 }
 
+// `which` tells the four instantiations apart (they share one function-pointer type).
 template <typename K>
-static int ensure_smem(K kern, int dev) {
+static int ensure_smem(K kern, int which, int dev) {
   static std::mutex mu;
-  static bool done[64] = {};
+  static bool done[4][64] = {};
   std::lock_guard<std::mutex> lock(mu);
-  if (dev >= 0 && dev < 64 && !done[dev]) {
+  if (dev >= 0 && dev < 64 && !done[which][dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes());
     if (e != cudaSuccess) return record_cuda_error(e);
-    done[dev] = true;
+    done[which][dev] = true;
   }
   return MUX_OK;
 }
@@ -459,11 +460,11 @@ int mux_tp_oproj_allreduce(const mux_tp_comm_t* comm, const mux_oproj_args_t* a,
   const CUtensorMap* none = nullptr;
   if (a->dtype == MUX_DTYPE_F16) {
     auto kern = oproj_allreduce_kernel<__half, false>;
-    if ((st = ensure_smem(kern, dev)) != MUX_OK) return st;
+    if ((st = ensure_smem(kern, 0, dev)) != MUX_OK) return st;
     e = cudaLaunchKernelEx(&cfg, kern, ma, mw, none, prm);
   } else {
     auto kern = oproj_allreduce_kernel<__nv_bfloat16, false>;
-    if ((st = ensure_smem(kern, dev)) != MUX_OK) return st;
+    if ((st = ensure_smem(kern, 1, dev)) != MUX_OK) return st;
     e = cudaLaunchKernelEx(&cfg, kern, ma, mw, none, prm);
   }
   return e == cudaSuccess ? MUX_OK : mux::record_cuda_error(e);
@@ -510,11 +511,11 @@ int mux_tp_oproj_allreduce_emulated(int32_t world, void* const* buffers, int64_t
   const void* fn;
   if (args[0].dtype == MUX_DTYPE_F16) {
     auto kern = oproj_allreduce_kernel<__half, true>;
-    if ((st = ensure_smem(kern, dev)) != MUX_OK) return st;
+    if ((st = ensure_smem(kern, 2, dev)) != MUX_OK) return st;
     fn = (const void*)kern;
   } else {
     auto kern = oproj_allreduce_kernel<__nv_bfloat16, true>;
-    if ((st = ensure_smem(kern, dev)) != MUX_OK) return st;
+    if ((st = ensure_smem(kern, 3, dev)) != MUX_OK) return st;
     fn = (const void*)kern;
   }
   // the ranks' CTAs wait on one another: the cooperative launch fails unless the whole grid is resident at once

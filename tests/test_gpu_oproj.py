@@ -66,7 +66,9 @@ def test_emulated_world_sums_the_rounded_partials_in_rank_order(env, world, dtyp
         want = acc.to(dtype)
         for r, o in enumerate(outs):
             assert torch.equal(o, want), f"world {world} call {call}: rank {r} differs"
-        assert _close(want, exact, dtype) or world > 2      # sanity against the exact product for small worlds
+        # and the whole thing stays near the exact fp32 product (each partial and the sum are rounded once)
+        eps = 2.0 ** (-8 if dtype == torch.bfloat16 else -11)
+        assert float((want.float() - exact).abs().max()) <= (world + 1) * eps * float(exact.abs().max()) + 1e-3
     assert ops.device_status() == 0
 
 

@@ -67,8 +67,28 @@ def _worker(rank, world, port, results):
     comm.all_reduce(partial, total)
     torch.cuda.synchronize()
     ok = ok and torch.equal(total.view(S, Hq, 128), whole)
+    # o_proj fused with the all-reduce: equals the rank-order sum of the ranks' rounded partial products
+    from muxserve_b200 import tp_comm
+    m, n, k = 96, 1024, 256
+    op = tp_comm.TPOProj(m, n, dev)
+    for dt in (torch.bfloat16, torch.float16):
+        g = torch.Generator().manual_seed(50 + rank)
+        a = torch.randn((m, k), generator=g).to(dt).to(dev)
+        w = (torch.randn((n, k), generator=g) / 16).to(dt).to(dev)
+        out, part = torch.empty((m, n), dtype=dt, device=dev), torch.empty((m, n), dtype=dt, device=dev)
+        tp_comm.oproj(a, w, part)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        acc = torch.zeros((m, n), dtype=torch.float32, device=dev)
+        for p_ in parts:
+            acc += p_.float()
+        for _ in range(3):
+            op.forward(a, w, out)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(out, acc.to(dt))
     ok = ok and ops.device_status() == 0
     results.put((rank, bool(ok)))
+    op.close()
     comm.close()
     dist.barrier()
     dist.destroy_process_group()
