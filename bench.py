@@ -1186,6 +1186,8 @@ def oproj_leg(env: Env, comm, name: str):
         return ms * 1e3 / L
 
     res["fused_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out), "fused o_proj")
+    res["fused_one_shot_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out, algo=1), "fused o_proj one-shot")
+    res["fused_two_shot_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out, algo=2), "fused o_proj owners")
     res["gemm_then_allreduce_us_per_layer"] = timed(lambda i: (tp_comm.oproj(a, wt[i], tmp), comm.all_reduce(tmp, out)),
                                                     "o_proj then all-reduce")
     res["cublas_then_nccl_us_per_layer"] = timed(lambda i: (torch.matmul(a, wt[i].T, out=tmp), dist.all_reduce(tmp)),

@@ -451,6 +451,8 @@ typedef struct {
   int64_t out_row_stride;
   int32_t m, n, k;
   int32_t dtype;
+  int32_t algo;        /* MUX_TP_AUTO, or force MUX_TP_ONE_SHOT (every rank sums every tile) / MUX_TP_TWO_SHOT (tile owners) */
+  int32_t reserved;
 } mux_oproj_args_t;
 int mux_tp_oproj_allreduce(const mux_tp_comm_t* comm, const mux_oproj_args_t* args, void* cuda_stream);
 /* All ranks of a world as one cooperative launch on ONE GPU (tests of the protocol): args[r] are rank r's

@@ -135,7 +135,7 @@ class TpComm(C.Structure):
 class OprojArgs(C.Structure):
     _fields_ = [("a", C.c_void_p), ("a_row_stride", C.c_int64), ("w", C.c_void_p), ("w_row_stride", C.c_int64),
                 ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
-                ("dtype", C.c_int32)]
+                ("dtype", C.c_int32), ("algo", C.c_int32), ("reserved", C.c_int32)]
 
 
 class MixedModel(C.Structure):

@@ -7,11 +7,14 @@
 // accumulators in tensor memory) whose epilogue is the exchange, tile by tile, so that the tiles that
 // finish first cross NVLink while the others still multiply:
 //
-//   CTA j owns output columns [64 j, 64 j + 64).  Rank j mod world is the tile's OWNER.
-//   1. every rank's CTA j rounds its partial tile to the tensor type and pushes it (plain peer stores)
-//      into the owner's exchange buffer, then raises a flag there;
-//   2. the owner's CTA j waits for the world's flags, sums the world's partial tiles from LOCAL memory
-//      in rank order (fp32), rounds once, pushes the sum to every rank and raises a second flag;
+//   CTA j owns output columns [64 j, 64 j + 64).  Small messages ((world - 1) * bytes <= 4 MiB) go one-shot:
+//   every rank's CTA j rounds its partial tile to the tensor type, pushes it (plain peer stores) into area
+//   [rank] of every rank's exchange buffer and raises a flag there; it then waits for the world's flags in
+//   its own buffer and sums the world's tiles from LOCAL memory in rank order (fp32, one rounding) into `out`.
+//   Larger messages go through the tile's OWNER, rank j mod world:
+//   1. every rank's CTA j pushes its partial tile into the owner's buffer and raises a flag there;
+//   2. the owner's CTA j waits for the world's flags, sums the world's partial tiles from local memory,
+//      pushes the sum to every rank and raises a second flag;
 //   3. every rank's CTA j waits for that flag and copies the 128 x 64 result to `out`.
 //
 // Flags carry a per-CTA call counter kept in the exchange buffer (every call on a communicator has the
@@ -39,7 +42,7 @@ constexpr int kBK = 64;                  // k elements per stage: one 128-byte s
 constexpr int kABytes = kBM * 128;       // 16 KiB
 constexpr int kBBytes = kBN * 128;       // 8 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kStages = 6;
+constexpr int kStages = 8;
 constexpr int kThreads = 192;            // warps 0-3 epilogue (one thread per row), 4 TMA producer, 5 MMA issuer
 constexpr int kProdWarp = 4, kMmaWarp = 5;
 constexpr uint32_t kTmemCols = 64;
@@ -64,6 +67,7 @@ struct Params {
   unsigned* status;
   int m, n, k;
   int world, rank;
+  int one_shot;                    // exchange form (see the top of the file)
 };
 
 constexpr int smem_bytes() { return kStages * kStageBytes + 1024 + 256; }
@@ -217,11 +221,17 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
   tmem = *slot;
 
   if (warp == kProdWarp) {
-    if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int st = kb % kStages;
-        if (kb >= kStages) mbar_wait_sleepy(bar(EMPTY + st), (uint32_t)(kb / kStages - 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
-        const uint32_t dst = raw + st * kStageBytes;
+    // lane s owns stage s (k-blocks s, s + kStages, ...): a single issuing thread pays the barrier and copy-issue
+    // latency of every stage in turn, which alone is longer than the weight stream of one CTA per SM needs
+    if (lane < kStages) {
+      const int st = lane;
+      const uint32_t dst = raw + st * kStageBytes;
+      uint32_t parity = 0;
+      for (int kb = st; kb < nkb; kb += kStages) {
+        if (kb >= kStages) {
+          mbar_wait_sleepy(bar(EMPTY + st), parity, p.status, MUX_DEV_WAIT_TIMEOUT);
+          parity ^= 1u;
+        }
         mbar_arrive_expect_tx(bar(FULL + st), kStageBytes);
         tma_load_2d(dst, tma_a, kb * kBK, 0, bar(FULL + st));                       // rows past m read as zeros
         tma_load_2d(dst + kABytes, tma_w, kb * kBK, tile * kBN, bar(FULL + st));
@@ -247,7 +257,7 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
   } else {
     // ------------------------------------------------------------------ epilogue: one thread per output row
     const int row = warp * 32 + lane;
-    mbar_wait(bar(ACC), 0, p.status, MUX_DEV_WAIT_TIMEOUT);
+    mbar_wait_sleepy(bar(ACC), 0, p.status, MUX_DEV_WAIT_TIMEOUT);  // 128 threads waiting out the whole main loop: asleep, not polling
     __syncwarp();
     tc_fence_after();
     float acc[64];
@@ -278,6 +288,39 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
       const size_t msg_bytes = (size_t)p.m * p.n * sizeof(T);
       const size_t cell = ((size_t)row * p.n + (size_t)tile * kBN) * sizeof(T);   // this row of this tile in a message
       const int owner = tile % p.world;
+      if (p.one_shot) {
+        if (live) {
+          for (int q = 0; q < p.world; ++q) {
+            uint4* dst = reinterpret_cast<uint4*>(p.buf[q] + slot_off + (size_t)rank * msg_bytes + cell);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = v[i];
+          }
+        }
+        named_bar_sync(1, 128);  // the releasing flag stores are cumulative over the rows pushed by the other threads
+        if (tid < p.world) st_flag(&reinterpret_cast<FusedCtrl*>(p.buf[tid] + kCtrlOffset)->ready[rank][tile], epoch);
+        if (tid < p.world) wait_flag(&my->ready[tid][tile], epoch, p.status);
+        named_bar_sync(1, 128);
+        if (live) {
+          const unsigned char* mine = p.buf[rank] + slot_off + cell;
+          uint4* dst = reinterpret_cast<uint4*>(out + (long long)row * p.out_stride[rank] + tile * kBN);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < p.world; ++q) {
+              const uint4 x = ld_vol(mine + (size_t)q * msg_bytes + 16 * i);
+              const float2 a = unpack2<T>(x.x), b = unpack2<T>(x.y), c = unpack2<T>(x.z), d = unpack2<T>(x.w);
+              s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
+            }
+            uint4 r;
+            r.x = pack2<T>(s[0], s[1]);
+            r.y = pack2<T>(s[2], s[3]);
+            r.z = pack2<T>(s[4], s[5]);
+            r.w = pack2<T>(s[6], s[7]);
+            dst[i] = r;
+          }
+        }
+        if (tid == 0) my->epoch[tile] = epoch;
+      } else {
       // 1. my partial tile -> the owner's area [rank]
       if (live) {
         uint4* dst = reinterpret_cast<uint4*>(p.buf[owner] + slot_off + (size_t)rank * msg_bytes + cell);
@@ -325,6 +368,7 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
         for (int i = 0; i < 8; ++i) dst[i] = ld_vol(src + 16 * i);
       }
       if (tid == 0) my->epoch[tile] = epoch;
+      }
     }
     tc_fence_before();
   }
@@ -376,6 +420,7 @@ static int validate(const mux_oproj_args_t* a) {
   if (a == nullptr) return MUX_ERR_NULL_POINTER;
   if (a->dtype != MUX_DTYPE_F16 && a->dtype != MUX_DTYPE_BF16) return MUX_ERR_BAD_DTYPE;
   if (a->m < 0 || a->m > kBM || a->n <= 0 || a->k <= 0) return MUX_ERR_BAD_SHAPE;
+  if (a->algo != MUX_TP_AUTO && a->algo != MUX_TP_ONE_SHOT && a->algo != MUX_TP_TWO_SHOT) return MUX_ERR_BAD_SHAPE;
   if (a->n % kBN != 0 || a->n > MUX_TP_OPROJ_MAX_COLS || a->k % kBK != 0) return MUX_ERR_BAD_SHAPE;
   if (a->m == 0) return MUX_OK;
   if (!a->a || !a->w || !a->out) return MUX_ERR_NULL_POINTER;
@@ -410,6 +455,9 @@ static int fill_exchange(Params& prm, int world, void* const* buffers, long long
   prm.slot_bytes = (buffer_bytes - (long long)kCtrlTotal) / 2 / 256 * 256;
   const size_t need = (size_t)world * a->m * a->n * 2;
   if (prm.slot_bytes <= 0 || need > (size_t)prm.slot_bytes) return MUX_ERR_TOO_LARGE;
+  prm.one_shot = a->algo == MUX_TP_ONE_SHOT   ? 1
+                 : a->algo == MUX_TP_TWO_SHOT ? 0
+                 : ((size_t)(world - 1) * a->m * a->n * 2 <= (size_t)MUX_TP_ONE_SHOT_MAX_PUSH_BYTES ? 1 : 0);
   return MUX_OK;
 }
 
@@ -478,7 +526,8 @@ int mux_tp_oproj_allreduce_emulated(int32_t world, void* const* buffers, int64_t
   int st;
   for (int q = 0; q < world; ++q) {
     if ((st = validate(&args[q])) != MUX_OK) return st;
-    if (args[q].m != args[0].m || args[q].n != args[0].n || args[q].k != args[0].k || args[q].dtype != args[0].dtype)
+    if (args[q].m != args[0].m || args[q].n != args[0].n || args[q].k != args[0].k || args[q].dtype != args[0].dtype ||
+        args[q].algo != args[0].algo)
       return MUX_ERR_BAD_SHAPE;
   }
   if (args[0].m == 0) return MUX_OK;

@@ -110,7 +110,7 @@ def all_reduce_emulated(inputs: List[torch.Tensor], max_message_bytes: Optional[
     return outs, buffers
 
 
-def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> "_lib.OprojArgs":
+def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int = _lib.MUX_TP_AUTO) -> "_lib.OprojArgs":
     if a.dim() != 2 or w.dim() != 2 or out.dim() != 2:
         raise ValueError("a [m, k], w [n, k] and out [m, n] must be 2-D")
     m, k = a.shape
@@ -123,7 +123,8 @@ def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> "_lib.Op
         if not t.is_cuda or t.stride(1) != 1:
             raise ValueError(f"{name} must be a CUDA tensor with a dense last dimension")
     return _lib.OprojArgs(a=a.data_ptr(), a_row_stride=a.stride(0), w=w.data_ptr(), w_row_stride=w.stride(0),
-                          out=out.data_ptr(), out_row_stride=out.stride(0), m=m, n=n, k=k, dtype=_DTYPES[a.dtype])
+                          out=out.data_ptr(), out_row_stride=out.stride(0), m=m, n=n, k=k, dtype=_DTYPES[a.dtype],
+                          algo=algo, reserved=0)
 
 
 def oproj(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -142,18 +143,19 @@ class TPOProj(TPAllReduce):
         super().__init__(max_tokens * hidden * 2, device, group)
         self.hidden = hidden
 
-    def forward(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int = _lib.MUX_TP_AUTO) -> torch.Tensor:
         """``out[t, n] = sum over ranks of round(a_rank[t, :] @ w_rank[n, :])``; ``a`` [tokens, local q heads * 128],
         ``w`` [hidden, local q heads * 128] (this rank's columns of the o_proj weight), ``out`` [tokens, hidden]."""
         if w.shape[0] != self.hidden:
             raise ValueError(f"this communicator was made for hidden size {self.hidden}")
-        args = _oproj_args(a, w, out)
+        args = _oproj_args(a, w, out, algo)
         check(lib().mux_tp_oproj_allreduce(C.byref(self.comm), C.byref(args), torch.cuda.current_stream().cuda_stream),
               "tp_oproj_allreduce")
         return out
 
 
-def oproj_allreduce_emulated(a_list: List[torch.Tensor], w_list: List[torch.Tensor], buffers=None):
+def oproj_allreduce_emulated(a_list: List[torch.Tensor], w_list: List[torch.Tensor], buffers=None,
+                             algo: int = _lib.MUX_TP_AUTO):
     """The fused kernel for ``len(a_list)`` ranks on ONE GPU (one cooperative launch); returns (outs, buffers)."""
     world = len(a_list)
     m, n = a_list[0].shape[0], w_list[0].shape[0]
@@ -162,7 +164,7 @@ def oproj_allreduce_emulated(a_list: List[torch.Tensor], w_list: List[torch.Tens
     if buffers is None:
         buffers = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
     outs = [torch.empty((m, n), dtype=a_list[0].dtype, device=dev) for _ in range(world)]
-    args = (_lib.OprojArgs * world)(*[_oproj_args(a, w, o) for a, w, o in zip(a_list, w_list, outs)])
+    args = (_lib.OprojArgs * world)(*[_oproj_args(a, w, o, algo) for a, w, o in zip(a_list, w_list, outs)])
     bufs = (C.c_void_p * world)(*[b.data_ptr() for b in buffers])
     scratch = torch.empty(2 * world * 128, dtype=torch.uint8, device=dev)
     check(lib().mux_tp_oproj_allreduce_emulated(world, bufs, nbytes, args, scratch.data_ptr(),

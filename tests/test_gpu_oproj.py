@@ -45,8 +45,9 @@ def test_gemm_alone_matches_torch(env, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("algo", [1, 2])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_emulated_world_sums_the_rounded_partials_in_rank_order(env, world, dtype):
+def test_emulated_world_sums_the_rounded_partials_in_rank_order(env, world, dtype, algo):
     ops, tp_comm = env
     m, n, k = 100, 512, 256
     gen = torch.Generator(device="cuda").manual_seed(world)
@@ -54,7 +55,7 @@ def test_emulated_world_sums_the_rounded_partials_in_rank_order(env, world, dtyp
     for call in range(3):                       # epochs advance, data areas alternate
         a_list = [torch.randn((m, k), generator=gen, device="cuda").to(dtype) for _ in range(world)]
         w_list = [(torch.randn((n, k), generator=gen, device="cuda") / k ** 0.5).to(dtype) for _ in range(world)]
-        outs, buffers = tp_comm.oproj_allreduce_emulated(a_list, w_list, buffers)
+        outs, buffers = tp_comm.oproj_allreduce_emulated(a_list, w_list, buffers, algo=algo)
         # every rank's partial through the same GEMM (bit-identical rounding), then the rank-order fp32 sum
         acc = torch.zeros((m, n), dtype=torch.float32, device="cuda")
         exact = torch.zeros((m, n), dtype=torch.float32, device="cuda")

@@ -82,10 +82,11 @@ def _worker(rank, world, port, results):
         acc = torch.zeros((m, n), dtype=torch.float32, device=dev)
         for p_ in parts:
             acc += p_.float()
-        for _ in range(3):
-            op.forward(a, w, out)
-        torch.cuda.synchronize()
-        ok = ok and torch.equal(out, acc.to(dt))
+        for algo in (0, 1, 2, 1):
+            out.zero_()
+            op.forward(a, w, out, algo=algo)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(out, acc.to(dt))
     ok = ok and ops.device_status() == 0
     results.put((rank, bool(ok)))
     op.close()
