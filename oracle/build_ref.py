@@ -7,6 +7,9 @@ reference checkout (they are never copied into this repository) with
 machine where the checkout is absent.
 
     python -m oracle.build_ref [/path/to/reference]
+
+Without an argument the checkout is looked for where ``MUXSERVE_REFERENCE`` points, else in a directory
+``reference`` beside this repository.
 """
 from __future__ import annotations
 
@@ -16,7 +19,7 @@ import sys
 from pathlib import Path
 
 REF_DIR = Path(__file__).resolve().parent / "_ref"
-DEFAULT_REFERENCE = Path(os.environ.get("MUXSERVE_REFERENCE", "/root/reference"))
+DEFAULT_REFERENCE = Path(os.environ.get("MUXSERVE_REFERENCE") or Path(__file__).resolve().parents[2] / "reference")
 MODULES = {"ref_memory_manager": "csrc/memory_manager.cpp", "ref_batch_scheduler": "csrc/batch_scheduler.cpp"}
 
 
