@@ -105,6 +105,8 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=0, help="prefill workload: every prompt has this length")
     ap.add_argument("--heads", type=int, default=0, help="prefill workload: override the head count (small captures)")
     ap.add_argument("--seed", type=int, default=20240531)
+    ap.add_argument("--block-size", type=int, default=16, choices=[16, 32],
+                    help="tokens per pool block for the whole run (16: the configurations' value; 32: MuxServe's default)")
     ap.add_argument("--eager", action="store_true",
                     help="time Python-issued launches instead of replaying a CUDA graph of one step")
     ap.add_argument("--two-op", action="store_true",
@@ -320,7 +322,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak" if args.gpus <= 1 else "strong", "vs_baseline": None,
         "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": f"{name}: {w['desc']}", "block_size": BLOCK, "seed": args.seed,
+        "config": {"workload": f"{name}: {w['desc']}".replace("block_size 16", f"block_size {BLOCK}"), "block_size": BLOCK, "seed": args.seed,
                    "ms_per_step_is": f"the measured time of one sampled step (1 layer, {seqs} sequences); a whole decode step "
                                      f"of the workload is {w['L']} x {w['S'] / seqs:.2f} times that",
                    "gpus_used": 0, "note_n_gpus": "the CPU arm runs on rank 0's host cores only and does not scale with N"},
@@ -434,6 +436,13 @@ class Pool:
         self.env = env
         self.desc = (f"{self.num_blocks} blocks = {self.num_blocks * 8192 / 1e9:.1f} GB ({args.pool_frac:.0%} of HBM), "
                      "block lists scattered without replacement over the whole pool")
+
+    def rebind(self, block_size: int):
+        """The same memory as a pool of `block_size`-token blocks (random contents stay valid under any view)."""
+        nb = self.kc.numel() // (128 * block_size)
+        self.kc = self.kc.reshape(-1)[:nb * 128 * block_size].view(nb, 16, block_size, 8)
+        self.vc = self.vc.reshape(-1)[:nb * 128 * block_size].view(nb, 128, block_size)
+        self.num_blocks = nb
 
     def as_dtype(self, dt):
         from muxserve_b200 import workloads
@@ -858,8 +867,11 @@ def run_c3(env: Env, pool: Pool, tp_world: int = 1, comm=None):
         span_ms = ms_step
     total = sum(attn_bytes) + (sum(cw_bytes) if fused else 0)
     achieved = total / (span_ms * 1e-3) / 1e9
+    traffic, traffic_src = ncu_traffic("c3", total) if not full else (None, "not captured for this shape")
     res["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                       "traffic": None, "kernel": "paged_attn_kernel<mixed, fused cache write> (+ merge)",
+                       "traffic": traffic, "traffic_source": traffic_src + ("; per STEP like algorithmic_bytes_per_step"
+                                                                           if traffic is not None else ""),
+                       "kernel": "paged_attn_kernel<mixed, fused cache write> (+ merge)",
                        "algorithmic_bytes_per_step": total, "attention_ms_per_step": span_ms, "peak_source": peak_src,
                        "span": "timed region of one step's attention launches (graph replay, one per layer index)"}
     if not args.no_parity:
@@ -1207,7 +1219,7 @@ def oproj_leg(env: Env, comm, name: str):
 
 # ----------------------------------------------------------------------------- orchestration
 def base_line(env, args, res, name, desc, dtype, scaling, placement, extra_cfg=None):
-    cfg = {"workload": f"{name}: {desc}", "block_size": BLOCK, "seed": args.seed,
+    cfg = {"workload": f"{name}: {desc}".replace("block_size 16", f"block_size {BLOCK}"), "block_size": BLOCK, "seed": args.seed,
            "l2": "no flush: every launch streams its own KV blocks, far more per step than the 126 MB L2 holds",
            "placement": placement}
     cfg.update(extra_cfg or {})
@@ -1220,6 +1232,22 @@ def base_line(env, args, res, name, desc, dtype, scaling, placement, extra_cfg=N
             "config": cfg, "roofline": res["roofline"], "timing": res["timing"], "step": res.get("step"),
             "parity_check": res.get("parity_check"), "clocks": res.get("clocks"), "device_status": env.status}
     return line
+
+
+def block32_leg(env: Env, pool: Pool):
+    """Configuration 2 over 32-token blocks (MuxServe's default block size, muxserve/arg_utils.py:22), on the same pool
+    memory; everything that reads the module's block size sees 32 for the duration."""
+    global BLOCK
+    BLOCK = 32
+    pool.rebind(32)
+    try:
+        keep = strip(run_decode(env, pool, "c2"))
+        return dict(workload="c2 with block_size 32: " + WORKLOADS["c2"]["desc"].replace("block_size 16", "block_size 32"),
+                    block_size=32, **keep)
+    finally:
+        BLOCK = 16
+        pool.rebind(16)
+        torch.cuda.empty_cache()
 
 
 def run_native_single(env: Env):
@@ -1262,6 +1290,9 @@ def run_native_single(env: Env):
                 configs[n] = dict(workload=f"{n}: {WORKLOADS[n]['desc']}", **strip(r))
                 del r
                 torch.cuda.empty_cache()
+            if BLOCK == 16:
+                log("c2 at block_size 32")
+                configs["c2_block32"] = block32_leg(env, pool)
             line["configs"] = configs
         line["device_status"] = env.status
         emit(line)
@@ -1380,7 +1411,9 @@ def run_native_tp(env: Env):
 
 
 def main():
+    global BLOCK
     args = parse_args()
+    BLOCK = args.block_size
     claim_stdout()
     if args.impl == "reference":
         run_reference(args)

@@ -255,7 +255,7 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
       umma_commit(bar(ACC));
     }
   } else {
-    // ------------------------------------------------------------------ epilogue: one thread per output row
+    // ------------------------------------------------------------------ epilogue: TMEM lane = output row
     const int row = warp * 32 + lane;
     mbar_wait_sleepy(bar(ACC), 0, p.status, MUX_DEV_WAIT_TIMEOUT);  // 128 threads waiting out the whole main loop: asleep, not polling
     __syncwarp();
@@ -273,101 +273,101 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
       v[i].z = pack2<T>(acc[8 * i + 4], acc[8 * i + 5]);
       v[i].w = pack2<T>(acc[8 * i + 6], acc[8 * i + 7]);
     }
-    const bool live = row < p.m;
     T* out = static_cast<T*>(p.out[rank]);
-    if (p.world == 1) {
-      if (live) {
-        uint4* dst = reinterpret_cast<uint4*>(out + (long long)row * p.out_stride[rank] + tile * kBN);
+    // The tile goes through shared memory (the operand stages are free once the accumulator barrier has fired) so
+    // that every global and peer access below is whole 128-byte rows: thread t then owns the 16-byte chunk
+    // c = t % 8 of rows t / 8 + 16 j.  Chunks are XOR-swizzled by row to keep both sides free of bank conflicts.
+    uint4* stg = reinterpret_cast<uint4*>(smem_raw);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dst[i] = v[i];
+    for (int i = 0; i < 8; ++i) stg[row * 8 + (i ^ (row & 7))] = v[i];
+    named_bar_sync(1, 128);
+    const int c = tid & 7, r0 = tid >> 3;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = j * 16 + r0;
+      v[j] = stg[r * 8 + (c ^ (r & 7))];
+    }
+    auto cell_of = [&](int j) {   // chunk (row j * 16 + r0, c) of this tile inside a [m, n] message
+      return ((size_t)(j * 16 + r0) * p.n + (size_t)tile * kBN) * sizeof(T) + (size_t)c * 16;
+    };
+    auto out_of = [&](int j) {
+      return reinterpret_cast<uint4*>(out + (long long)(j * 16 + r0) * p.out_stride[rank] + tile * kBN) + c;
+    };
+    auto sum_world = [&](const unsigned char* base, int j) {   // fixed rank order: every rank gets the same bits
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int q = 0; q < p.world; ++q) {
+        const uint4 x = ld_vol(base + (size_t)q * ((size_t)p.m * p.n * sizeof(T)) + cell_of(j));
+        const float2 a = unpack2<T>(x.x), b = unpack2<T>(x.y), cc = unpack2<T>(x.z), d = unpack2<T>(x.w);
+        s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += cc.x; s[5] += cc.y; s[6] += d.x; s[7] += d.y;
       }
+      uint4 r;
+      r.x = pack2<T>(s[0], s[1]);
+      r.y = pack2<T>(s[2], s[3]);
+      r.z = pack2<T>(s[4], s[5]);
+      r.w = pack2<T>(s[6], s[7]);
+      return r;
+    };
+    const int nj = (p.m - r0 + 15) / 16;   // rows j * 16 + r0 < m
+    if (p.world == 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < nj) *out_of(j) = v[j];
     } else {
       FusedCtrl* my = reinterpret_cast<FusedCtrl*>(p.buf[rank] + kCtrlOffset);
       const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&my->epoch[tile]) + 1u;
       const size_t slot_off = kCtrlTotal + (size_t)(epoch & 1u) * (size_t)p.slot_bytes;
       const size_t msg_bytes = (size_t)p.m * p.n * sizeof(T);
-      const size_t cell = ((size_t)row * p.n + (size_t)tile * kBN) * sizeof(T);   // this row of this tile in a message
       const int owner = tile % p.world;
       if (p.one_shot) {
-        if (live) {
-          for (int q = 0; q < p.world; ++q) {
-            uint4* dst = reinterpret_cast<uint4*>(p.buf[q] + slot_off + (size_t)rank * msg_bytes + cell);
+        for (int q = 0; q < p.world; ++q) {
+          unsigned char* dst = p.buf[q] + slot_off + (size_t)rank * msg_bytes;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = v[i];
-          }
+          for (int j = 0; j < 8; ++j)
+            if (j < nj) *reinterpret_cast<uint4*>(dst + cell_of(j)) = v[j];
         }
-        named_bar_sync(1, 128);  // the releasing flag stores are cumulative over the rows pushed by the other threads
+        named_bar_sync(1, 128);  // the releasing flag stores are cumulative over the chunks pushed by the other threads
         if (tid < p.world) st_flag(&reinterpret_cast<FusedCtrl*>(p.buf[tid] + kCtrlOffset)->ready[rank][tile], epoch);
         if (tid < p.world) wait_flag(&my->ready[tid][tile], epoch, p.status);
         named_bar_sync(1, 128);
-        if (live) {
-          const unsigned char* mine = p.buf[rank] + slot_off + cell;
-          uint4* dst = reinterpret_cast<uint4*>(out + (long long)row * p.out_stride[rank] + tile * kBN);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int q = 0; q < p.world; ++q) {
-              const uint4 x = ld_vol(mine + (size_t)q * msg_bytes + 16 * i);
-              const float2 a = unpack2<T>(x.x), b = unpack2<T>(x.y), c = unpack2<T>(x.z), d = unpack2<T>(x.w);
-              s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
-            }
-            uint4 r;
-            r.x = pack2<T>(s[0], s[1]);
-            r.y = pack2<T>(s[2], s[3]);
-            r.z = pack2<T>(s[4], s[5]);
-            r.w = pack2<T>(s[6], s[7]);
-            dst[i] = r;
-          }
-        }
+        for (int j = 0; j < 8; ++j)
+          if (j < nj) *out_of(j) = sum_world(p.buf[rank] + slot_off, j);
         if (tid == 0) my->epoch[tile] = epoch;
       } else {
-      // 1. my partial tile -> the owner's area [rank]
-      if (live) {
-        uint4* dst = reinterpret_cast<uint4*>(p.buf[owner] + slot_off + (size_t)rank * msg_bytes + cell);
+        // 1. my partial tile -> the owner's area [rank]
+        {
+          unsigned char* dst = p.buf[owner] + slot_off + (size_t)rank * msg_bytes;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dst[i] = v[i];
-      }
-      named_bar_sync(1, 128);  // the releasing flag store is cumulative over the rows pushed by the other threads
-      if (tid == 0) st_flag(&reinterpret_cast<FusedCtrl*>(p.buf[owner] + kCtrlOffset)->ready[rank][tile], epoch);
-      // 2. the owner sums the world's partial tiles and hands the sum to everybody
-      if (owner == rank) {
-        if (tid < p.world) wait_flag(&my->ready[tid][tile], epoch, p.status);
-        named_bar_sync(1, 128);
-        if (live) {
-          const unsigned char* mine = p.buf[rank] + slot_off + cell;
+          for (int j = 0; j < 8; ++j)
+            if (j < nj) *reinterpret_cast<uint4*>(dst + cell_of(j)) = v[j];
+        }
+        named_bar_sync(1, 128);  // the releasing flag store is cumulative over the chunks pushed by the other threads
+        if (tid == 0) st_flag(&reinterpret_cast<FusedCtrl*>(p.buf[owner] + kCtrlOffset)->ready[rank][tile], epoch);
+        // 2. the owner sums the world's partial tiles and hands the sum to everybody
+        if (owner == rank) {
+          if (tid < p.world) wait_flag(&my->ready[tid][tile], epoch, p.status);
+          named_bar_sync(1, 128);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int q = 0; q < p.world; ++q) {
-              const uint4 x = ld_vol(mine + (size_t)q * msg_bytes + 16 * i);
-              const float2 a = unpack2<T>(x.x), b = unpack2<T>(x.y), c = unpack2<T>(x.z), d = unpack2<T>(x.w);
-              s[0] += a.x; s[1] += a.y; s[2] += b.x; s[3] += b.y; s[4] += c.x; s[5] += c.y; s[6] += d.x; s[7] += d.y;
-            }
-            v[i].x = pack2<T>(s[0], s[1]);
-            v[i].y = pack2<T>(s[2], s[3]);
-            v[i].z = pack2<T>(s[4], s[5]);
-            v[i].w = pack2<T>(s[6], s[7]);
-          }
+          for (int j = 0; j < 8; ++j)
+            if (j < nj) v[j] = sum_world(p.buf[rank] + slot_off, j);
           // the sum goes where the owner's own partial lay, on every rank (elsewhere that cell is unused)
           for (int q = 0; q < p.world; ++q) {
-            uint4* dst = reinterpret_cast<uint4*>(p.buf[q] + slot_off + (size_t)rank * msg_bytes + cell);
+            unsigned char* dst = p.buf[q] + slot_off + (size_t)rank * msg_bytes;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = v[i];
+            for (int j = 0; j < 8; ++j)
+              if (j < nj) *reinterpret_cast<uint4*>(dst + cell_of(j)) = v[j];
           }
+          named_bar_sync(1, 128);
+          if (tid < p.world) st_flag(&reinterpret_cast<FusedCtrl*>(p.buf[tid] + kCtrlOffset)->done[tile], epoch);
         }
+        // 3. everybody takes the sum from its own buffer
+        if (tid == 0) wait_flag(&my->done[tile], epoch, p.status);
         named_bar_sync(1, 128);
-        if (tid < p.world) st_flag(&reinterpret_cast<FusedCtrl*>(p.buf[tid] + kCtrlOffset)->done[tile], epoch);
-      }
-      // 3. everybody takes the sum from its own buffer
-      if (tid == 0) wait_flag(&my->done[tile], epoch, p.status);
-      named_bar_sync(1, 128);
-      if (live) {
-        const unsigned char* src = p.buf[rank] + slot_off + (size_t)owner * msg_bytes + cell;
-        uint4* dst = reinterpret_cast<uint4*>(out + (long long)row * p.out_stride[rank] + tile * kBN);
+        const unsigned char* src = p.buf[rank] + slot_off + (size_t)owner * msg_bytes;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dst[i] = ld_vol(src + 16 * i);
-      }
-      if (tid == 0) my->epoch[tile] = epoch;
+        for (int j = 0; j < 8; ++j)
+          if (j < nj) *out_of(j) = ld_vol(src + cell_of(j));
+        if (tid == 0) my->epoch[tile] = epoch;
       }
     }
     tc_fence_before();
