@@ -220,6 +220,12 @@ __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // ---- prompt cache write from the staged steps ------------------------------------------------
 // The CTA of query tile qt holds the K and V steps 2 qt and 2 qt + 1 (its own rows' tokens) in shared memory at
 // the end of its walk; the q head that comes first in its group copies them to the pool: the two producer warps,
@@ -589,10 +595,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
 #pragma unroll
       for (int i = 0; i < 4; ++i) mx4[i] = s[i];
 #pragma unroll
-      for (int c = 4; c < kStep; c += 4)
+      for (int c = 4; c < kStep - 4; c += 8)   // three-input maximum: half the instructions of a two-input chain
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], s[c + i]);
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
+        for (int i = 0; i < 4; ++i) mx4[i] = fmax3(mx4[i], s[c + i], s[c + 4 + i]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], s[kStep - 4 + i]);
+      const float mx = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]) * sl2;
       // Lazy rescaling: the reference point of the exponentials moves only when the row maximum grew by more
       // than 2^8; until then weights up to 256 are exact enough in 16 bits and O needs no correction.
       const bool grow = mx > m_run + kRescaleStep;
