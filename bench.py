@@ -1197,14 +1197,15 @@ def oproj_leg(env: Env, comm, name: str):
         ms, _ = env.timed(run, env.args.steps, 3, target_s=0.3)
         return ms * 1e3 / L
 
-    res["fused_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out), "fused o_proj")
+    res["fused_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out, early_w=True), "fused o_proj")
+    res["fused_no_early_w_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out), "fused o_proj, no early weights")
     res["fused_one_shot_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out, algo=1), "fused o_proj one-shot")
     res["fused_two_shot_us_per_layer"] = timed(lambda i: op.forward(a, wt[i], out, algo=2), "fused o_proj owners")
-    res["gemm_then_allreduce_us_per_layer"] = timed(lambda i: (tp_comm.oproj(a, wt[i], tmp), comm.all_reduce(tmp, out)),
+    res["gemm_then_allreduce_us_per_layer"] = timed(lambda i: (tp_comm.oproj(a, wt[i], tmp, early_w=True), comm.all_reduce(tmp, out)),
                                                     "o_proj then all-reduce")
     res["cublas_then_nccl_us_per_layer"] = timed(lambda i: (torch.matmul(a, wt[i].T, out=tmp), dist.all_reduce(tmp)),
                                                  "cuBLAS then NCCL")
-    res["gemm_alone_us_per_layer"] = timed(lambda i: tp_comm.oproj(a, wt[i], tmp), "o_proj alone")
+    res["gemm_alone_us_per_layer"] = timed(lambda i: tp_comm.oproj(a, wt[i], tmp, early_w=True), "o_proj alone")
     flops, wbytes = 2.0 * m * hidden * k, hidden * k * 2
     link = 2.0 * (world - 1) / world * m * hidden * 2
     peak_t, _ = tensor_peak()

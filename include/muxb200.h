@@ -442,6 +442,10 @@ int mux_tp_allreduce(const mux_tp_comm_t* comm, const void* in, void* out, int64
  * order (its exchange buffer: mux_tp_allreduce_buffer_size(world, m_max * n * 2)).
  * ---------------------------------------------------------------------- */
 #define MUX_TP_OPROJ_MAX_COLS 16384
+/* The caller states that `w` is not written by the kernels directly ahead in the stream (model weights never are):
+ * the launch is made programmatically dependent and starts streaming the first weight tiles while those kernels
+ * drain; `a`, the exchange buffers and `out` are touched only after they have completed. */
+#define MUX_OPROJ_EARLY_W 1
 typedef struct {
   const void* a;
   int64_t a_row_stride;
@@ -452,7 +456,7 @@ typedef struct {
   int32_t m, n, k;
   int32_t dtype;
   int32_t algo;        /* MUX_TP_AUTO, or force MUX_TP_ONE_SHOT (every rank sums every tile) / MUX_TP_TWO_SHOT (tile owners) */
-  int32_t reserved;
+  int32_t flags;       /* 0 or MUX_OPROJ_EARLY_W */
 } mux_oproj_args_t;
 int mux_tp_oproj_allreduce(const mux_tp_comm_t* comm, const mux_oproj_args_t* args, void* cuda_stream);
 /* All ranks of a world as one cooperative launch on ONE GPU (tests of the protocol): args[r] are rank r's

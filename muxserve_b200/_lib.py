@@ -23,10 +23,11 @@ MUX_DEV_INTERNAL = 32
 MUX_DEV_BAD_GROUP = 64
 
 MUX_ATTN_EARLY_KV = 1
+MUX_OPROJ_EARLY_W = 1
 
 MUX_TP_AUTO, MUX_TP_ONE_SHOT, MUX_TP_TWO_SHOT = 0, 1, 2
 
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 
 class CacheWriteArgs(C.Structure):
@@ -135,7 +136,7 @@ class TpComm(C.Structure):
 class OprojArgs(C.Structure):
     _fields_ = [("a", C.c_void_p), ("a_row_stride", C.c_int64), ("w", C.c_void_p), ("w_row_stride", C.c_int64),
                 ("out", C.c_void_p), ("out_row_stride", C.c_int64), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
-                ("dtype", C.c_int32), ("algo", C.c_int32), ("reserved", C.c_int32)]
+                ("dtype", C.c_int32), ("algo", C.c_int32), ("flags", C.c_int32)]
 
 
 class MixedModel(C.Structure):

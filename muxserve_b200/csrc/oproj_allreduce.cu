@@ -68,6 +68,7 @@ struct Params {
   int m, n, k;
   int world, rank;
   int one_shot;                    // exchange form (see the top of the file)
+  int early_w;                     // weight tiles may be fetched before the kernels ahead have completed
 };
 
 constexpr int smem_bytes() { return kStages * kStageBytes + 1024 + 256; }
@@ -209,8 +210,9 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
     mbar_init(bar(ACC), 1);
     mbar_init_fence();
   }
-  // the weight slice is a constant of the model; the activations and the call counter come from the kernels ahead
-  griddep_wait();
+  // The weight slice is a constant of the model; the activations and the call counter come from the kernels ahead.
+  // With early_w only the threads that touch those (producer lanes before their first A tile, the epilogue) wait.
+  if (!p.early_w) griddep_wait();
   griddep_launch_dependents();
   __syncthreads();
   uint32_t tmem = 0;
@@ -233,8 +235,9 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
           parity ^= 1u;
         }
         mbar_arrive_expect_tx(bar(FULL + st), kStageBytes);
-        tma_load_2d(dst, tma_a, kb * kBK, 0, bar(FULL + st));                       // rows past m read as zeros
         tma_load_2d(dst + kABytes, tma_w, kb * kBK, tile * kBN, bar(FULL + st));
+        if (p.early_w && kb == st) griddep_wait();
+        tma_load_2d(dst, tma_a, kb * kBK, 0, bar(FULL + st));                       // rows past m read as zeros
       }
     }
   } else if (warp == kMmaWarp) {
@@ -257,6 +260,7 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
   } else {
     // ------------------------------------------------------------------ epilogue: TMEM lane = output row
     const int row = warp * 32 + lane;
+    if (p.early_w) griddep_wait();
     mbar_wait_sleepy(bar(ACC), 0, p.status, MUX_DEV_WAIT_TIMEOUT);  // 128 threads waiting out the whole main loop: asleep, not polling
     __syncwarp();
     tc_fence_after();
@@ -421,6 +425,7 @@ static int validate(const mux_oproj_args_t* a) {
   if (a->dtype != MUX_DTYPE_F16 && a->dtype != MUX_DTYPE_BF16) return MUX_ERR_BAD_DTYPE;
   if (a->m < 0 || a->m > kBM || a->n <= 0 || a->k <= 0) return MUX_ERR_BAD_SHAPE;
   if (a->algo != MUX_TP_AUTO && a->algo != MUX_TP_ONE_SHOT && a->algo != MUX_TP_TWO_SHOT) return MUX_ERR_BAD_SHAPE;
+  if ((a->flags & ~MUX_OPROJ_EARLY_W) != 0) return MUX_ERR_BAD_SHAPE;
   if (a->n % kBN != 0 || a->n > MUX_TP_OPROJ_MAX_COLS || a->k % kBK != 0) return MUX_ERR_BAD_SHAPE;
   if (a->m == 0) return MUX_OK;
   if (!a->a || !a->w || !a->out) return MUX_ERR_NULL_POINTER;
@@ -483,6 +488,7 @@ int mux_tp_oproj_allreduce(const mux_tp_comm_t* comm, const mux_oproj_args_t* a,
   prm.m = a->m;
   prm.n = a->n;
   prm.k = a->k;
+  prm.early_w = (a->flags & MUX_OPROJ_EARLY_W) ? 1 : 0;
   prm.out[prm.rank] = a->out;
   prm.out_stride[prm.rank] = a->out_row_stride;
   prm.status = mux::device_status_ptr();

@@ -80,7 +80,7 @@ const char* mux_strerror(int status) {
 
 int mux_last_cuda_error(void) { return g_last_cuda_error; }
 
-int mux_abi_version(void) { return 15; }
+int mux_abi_version(void) { return 16; }
 
 int mux_selftest_wait_timeout(void* cuda_stream) {
   unsigned* p = mux::device_status_ptr();

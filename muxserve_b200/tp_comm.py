@@ -110,7 +110,8 @@ def all_reduce_emulated(inputs: List[torch.Tensor], max_message_bytes: Optional[
     return outs, buffers
 
 
-def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int = _lib.MUX_TP_AUTO) -> "_lib.OprojArgs":
+def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int = _lib.MUX_TP_AUTO,
+                early_w: bool = False) -> "_lib.OprojArgs":
     if a.dim() != 2 or w.dim() != 2 or out.dim() != 2:
         raise ValueError("a [m, k], w [n, k] and out [m, n] must be 2-D")
     m, k = a.shape
@@ -124,12 +125,13 @@ def _oproj_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int =
             raise ValueError(f"{name} must be a CUDA tensor with a dense last dimension")
     return _lib.OprojArgs(a=a.data_ptr(), a_row_stride=a.stride(0), w=w.data_ptr(), w_row_stride=w.stride(0),
                           out=out.data_ptr(), out_row_stride=out.stride(0), m=m, n=n, k=k, dtype=_DTYPES[a.dtype],
-                          algo=algo, reserved=0)
+                          algo=algo, flags=_lib.MUX_OPROJ_EARLY_W if early_w else 0)
 
 
-def oproj(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """``out = a @ w.T`` on the tcgen05 GEMM of the fused kernel, without any exchange (one rank)."""
-    args = _oproj_args(a, w, out)
+def oproj(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, early_w: bool = False) -> torch.Tensor:
+    """``out = a @ w.T`` on the tcgen05 GEMM of the fused kernel, without any exchange (one rank).  ``early_w``:
+    ``w`` is not written by the kernels directly ahead in the stream, so its first tiles may stream while they drain."""
+    args = _oproj_args(a, w, out, early_w=early_w)
     check(lib().mux_tp_oproj_allreduce(None, C.byref(args), torch.cuda.current_stream().cuda_stream), "tp_oproj")
     return out
 
@@ -143,12 +145,13 @@ class TPOProj(TPAllReduce):
         super().__init__(max_tokens * hidden * 2, device, group)
         self.hidden = hidden
 
-    def forward(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int = _lib.MUX_TP_AUTO) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: int = _lib.MUX_TP_AUTO,
+                early_w: bool = False) -> torch.Tensor:
         """``out[t, n] = sum over ranks of round(a_rank[t, :] @ w_rank[n, :])``; ``a`` [tokens, local q heads * 128],
         ``w`` [hidden, local q heads * 128] (this rank's columns of the o_proj weight), ``out`` [tokens, hidden]."""
         if w.shape[0] != self.hidden:
             raise ValueError(f"this communicator was made for hidden size {self.hidden}")
-        args = _oproj_args(a, w, out, algo)
+        args = _oproj_args(a, w, out, algo, early_w)
         check(lib().mux_tp_oproj_allreduce(C.byref(self.comm), C.byref(args), torch.cuda.current_stream().cuda_stream),
               "tp_oproj_allreduce")
         return out

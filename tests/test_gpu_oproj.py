@@ -41,6 +41,19 @@ def test_gemm_alone_matches_torch(env, dtype, m, n, k):
     big_o = torch.zeros((m, n + 8), dtype=dtype, device="cuda")
     tp_comm.oproj(big_a[:, :k], w, big_o[:, :n])
     assert torch.equal(big_o[:, :n], out) and float(big_o[:, n:].abs().sum()) == 0.0
+    # early weights: a chain of launches whose activations are each written by the kernel directly ahead
+    chain = []
+    for i in range(4):
+        a_i = torch.empty_like(a)
+        o_i = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+        a_i.copy_(a).mul_(i + 1)                      # the producer of this launch's activations
+        tp_comm.oproj(a_i, w, o_i, early_w=True)
+        chain.append((a_i, o_i))
+    torch.cuda.synchronize()
+    for a_i, o_i in chain:
+        ref_i = torch.empty_like(o_i)
+        tp_comm.oproj(a_i, w, ref_i)
+        assert torch.equal(o_i, ref_i), "early weight fetch changed the result"
     assert ops.device_status() == 0
 
 
@@ -89,7 +102,7 @@ def test_argument_errors(env):
     assert call() == 0
     assert call(m=129) == -6 and call(n=96) == -6 and call(k=32) == -6 and call(dtype=5) == -2
     assert call(a_row_stride=63) == -5 and call(out_row_stride=8) == -6
-    assert call(a=None) == -1
+    assert call(a=None) == -1 and call(flags=2) == -6 and call(flags=1) == 0
     with pytest.raises(ValueError):
         tp_comm.oproj(a, w[:, :32], o)
     assert ops.device_status() == 0
