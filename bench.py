@@ -582,7 +582,8 @@ def run_decode(env: Env, pool: Pool, name: str, tp: int = 1, tp_rank: int = 0, h
     peak, peak_src = hbm_peak()
     launch_bytes = attn_bytes + (cw_bytes if fused else 0)
     achieved = launch_bytes / (attn_ms * 1e-3) / 1e9
-    traffic, traffic_src = ncu_traffic(name, launch_bytes) if tp == 1 and args.batch == 0 else (None, "not captured for this shape")
+    traffic, traffic_src = (ncu_traffic(name, launch_bytes) if tp == 1 and args.batch == 0 and BLOCK == 16
+                            else (None, "not captured for this shape"))
     res["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                        "traffic": traffic, "traffic_source": traffic_src,
                        "kernel": ("paged_attn_kernel<fused cache write> (+ merge kernel)" if fused else
