@@ -67,6 +67,7 @@ struct Params {
   const long long* slots;
   long long s_ts, s_hs, num_blocks;
   int block_size;
+  int bs_shift;                             // log2(block_size): 8, 16 or 32 tokens, so slot -> (block, offset) is a shift
   const int* bt;                            // block lists instead of slots (slots == nullptr)
   long long bt_ss, bt_hs;
   int max_blocks;
@@ -240,7 +241,7 @@ __device__ __forceinline__ long long step_slot(const Params& p, int seq, int sta
   if (p.slots != nullptr) {
     slot = p.slots[(long long)(start + pos) * p.s_ts + (long long)kvh * p.s_hs];
   } else {  // from the block list of (prompt, kv head)
-    const int b = pos / p.block_size;
+    const int b = pos >> p.bs_shift;
     if (b >= p.max_blocks) {
       atomicOr(p.status, MUX_DEV_BAD_CONTEXT);
       return -1;
@@ -249,7 +250,7 @@ __device__ __forceinline__ long long step_slot(const Params& p, int seq, int sta
     slot = id < 0 ? -1 : id * p.block_size + (pos - b * p.block_size);
   }
   if (slot < 0) return -1;
-  if (slot / p.block_size >= p.num_blocks) {
+  if ((slot >> p.bs_shift) >= p.num_blocks) {
     atomicOr(p.status, MUX_DEV_BAD_SLOT);
     return -1;
   }
@@ -268,13 +269,18 @@ __device__ __forceinline__ void copy_k_step(const Params& p, uint32_t tile, cons
     const int r = half * 32 + lane;
     const long long slot = slots[r];
     if (slot < 0) continue;
-    const long long blk = slot / BS;
+    const long long blk = slot >> p.bs_shift;
     T* dst = static_cast<T*>(p.kc) + blk * (128 * BS) + (slot - blk * BS) * 8;
     const uint32_t src = tile + (uint32_t)r * 128u;
-#pragma unroll 4
-    for (int c = 0; c < 16; ++c) {
-      const uint4 w = lds128(src + (uint32_t)(c >> 3) * kSlabBytes + (uint32_t)(((c & 7) ^ (r & 7)) << 4));
-      *reinterpret_cast<uint4*>(dst + c * (BS * 8)) = w;
+    // all of a slab's loads first, then its stores: a store directly behind its load makes every piece wait out
+    // a shared-memory round trip (the loads are ordered asm statements; one at a time they took ~75 cycles each)
+#pragma unroll
+    for (int slab = 0; slab < 2; ++slab) {
+      uint4 w[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) w[c] = lds128(src + (uint32_t)slab * kSlabBytes + (uint32_t)((c ^ (r & 7)) << 4));
+#pragma unroll
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + (slab * 8 + c) * (BS * 8)) = w[c];
     }
   }
 }
@@ -300,27 +306,29 @@ __device__ __forceinline__ void copy_v_groups(const Params& p, uint32_t tile, co
     const bool run = base >= 0 && (base & 7) == 0 && ((good >> l0) & 0xffu) == 0xffu;
     const int r0 = g * 8;
     if (run) {
-      const long long blk = base / BS;
+      const long long blk = base >> p.bs_shift;
       // this lane's destination inside a piece: d = lane / 4 of the piece, tokens 2 (lane % 4), + 1
       unsigned short* dst = vc + blk * (128 * BS) + (base - blk * BS) + (long long)(lane >> 2) * BS + 2 * (lane & 3);
       const int r = r0 + (lane & 7);  // the row whose 16-byte piece this lane names to ldmatrix
       const uint32_t rowaddr = tile + (uint32_t)r * 128u;
+      uint32_t m[4][4];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {  // pieces (d chunks) 4 q4 .. 4 q4 + 3, one per lane octet
+      for (int q4 = 0; q4 < 4; ++q4) {  // pieces (d chunks) 4 q4 .. 4 q4 + 3, one per lane octet; loads first (see K)
         const int c = 4 * q4 + (lane >> 3);
-        uint32_t m[4];
-        ldmatrix_x4_trans(m, rowaddr + (uint32_t)(c >> 3) * kSlabBytes + (uint32_t)(((c & 7) ^ (r & 7)) << 4));
+        ldmatrix_x4_trans(m[q4], rowaddr + (uint32_t)(c >> 3) * kSlabBytes + (uint32_t)(((c & 7) ^ (r & 7)) << 4));
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4)
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint32_t*>(dst + (long long)(8 * (4 * q4 + i)) * BS) = m[i];
-      }
+          *reinterpret_cast<uint32_t*>(dst + (long long)(8 * (4 * q4 + i)) * BS) = m[q4][i];
     } else {
 #pragma unroll 1
       for (int i = 0; i < 8; ++i) {
         const long long slot = __shfl_sync(0xffffffffu, mine, l0 + i);
         if (slot < 0) continue;  // the same for every lane
         const int r = r0 + i;
-        const long long blk = slot / BS;
+        const long long blk = slot >> p.bs_shift;
         unsigned short* dst = vc + blk * (128 * BS) + (slot - blk * BS);
 #pragma unroll 1
         for (int pass = 0; pass < 4; ++pass) {
@@ -338,7 +346,7 @@ __device__ __forceinline__ void copy_v_groups(const Params& p, uint32_t tile, co
   }
 }
 
-constexpr int kVGroupsOfVWarp = 5;  // of the 8 groups of a step; the K warp, which also copies K, takes the rest
+constexpr int kVGroupsOfVWarp = 4;  // of the 8 groups of a step; the K warp, which also copies K but starts earlier, takes the rest
 
 // ---- the kernel ------------------------------------------------------------------------------
 //
@@ -454,14 +462,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
     tmem = *slot;
   }
 
-  long long* sslots = reinterpret_cast<long long*>(smem_raw + (sBar + 256 - raw));  // [2 steps][64 rows]
-  if (write_pool && (warp == kKWarp || warp == kVWarp) && lane > 0) {
-    // the idle lanes of the producer warps fetch the slots of this tile's 128 tokens (K warp: step 2 qt, V warp:
-    // step 2 qt + 1) while the first copies are in flight
-    const int which = warp == kKWarp ? 0 : 1;
-    for (int r = lane - 1; r < kStep; r += 31)
-      sslots[which * kStep + r] = step_slot(p, seq, start, len, kvh, first_masked + which, r);
-  }
+  // The slots of this tile's 128 tokens ([2 steps][64 rows]) are fetched by the softmax threads, one each, while they
+  // wait for the first logits; each producer warp meets them at a named barrier of its own before its first copy.  (Fetched
+  // by the producer warps' idle lanes, ahead of or beside lane 0's loop, the DRAM round trips held lane 0 up.)
+  long long* sslots = reinterpret_cast<long long*>(smem_raw + (sBar + 256 - raw));
   if (warp == kKWarp) {
     // ------------------------------------------------------------------ TMA producer: the later K steps
     if (lane == 0) {
@@ -476,7 +480,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       }
     }
     __syncwarp();
-    if (write_pool) named_bar_sync(4, 64);  // both producer warps: all 128 slots are in shared memory
+    if (write_pool) named_bar_sync(4, 32 + kSoftmaxWarps * 32);  // the slots are in shared memory (K warp's barrier)
     // The last steps: no copy of this CTA may still be in flight when it ends (matters only after a failed
     // wait), and the steps of this tile's own tokens (2 qt and 2 qt + 1, never overwritten) go to the pool.
     for (int j = (n > kStages ? n - kStages : 0); j < n; ++j) {
@@ -484,8 +488,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       __syncwarp();
       if (write_pool && j >= first_masked) {
         copy_k_step<T>(p, sK + (j & 1) * kStepBytes, sslots + (j - first_masked) * kStep, lane);
-        named_bar_sync(2 + (j & 1), 64);  // the V warp has seen this step's V land (one barrier per step: its 32
-                                          // arrivals and this warp's 32 make 64 whichever side comes first)
+        // this warp is done with its copies of K long before the V warp, whose last copy waits for P.V of step
+        // n - 3: it takes its share of the step's V as soon as that has landed
+        mbar_wait_sleepy(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
+        __syncwarp();
         copy_v_groups<T>(p, sV + (j & 1) * kStepBytes, sslots + (j - first_masked) * kStep, lane, kVGroupsOfVWarp, 8);
       }
     }
@@ -503,12 +509,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
       }
     }
     __syncwarp();
-    if (write_pool) named_bar_sync(4, 64);
+    if (write_pool) named_bar_sync(5, 32 + kSoftmaxWarps * 32);  // the slots are in shared memory (V warp's barrier)
     for (int j = (n > kStages ? n - kStages : 0); j < n; ++j) {
       mbar_wait_sleepy(bar(V_FULL + (j & 1)), (uint32_t)(j >> 1) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
       __syncwarp();
       if (write_pool && j >= first_masked) {
-        named_bar_arrive(2 + (j & 1), 64);  // lets the K warp take its share of this step's V
         copy_v_groups<T>(p, sV + (j & 1) * kStepBytes, sslots + (j - first_masked) * kStep, lane, 0, kVGroupsOfVWarp);
       }
     }
@@ -570,6 +575,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_consta
   } else {
     // ------------------------------------------------------------------ softmax: one thread per query row
     const int row = tid;  // = TMEM lane; warp w reads lanes 32 w ...
+    if (write_pool) {
+      sslots[row] = step_slot(p, seq, start, len, kvh, first_masked + (row >> 6), row & (kStep - 1));
+      named_bar_arrive(4, 32 + kSoftmaxWarps * 32);  // one barrier per producer warp: neither waits for the other
+      named_bar_arrive(5, 32 + kSoftmaxWarps * 32);
+    }
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
     const uint32_t tO = lane_base + 128;
     const float sl2 = p.scale_log2;
@@ -825,6 +835,7 @@ static int run(const mux_prefill_args_t* a, cudaStream_t stream) {
   prm.s_hs = a->slot_head_stride;
   prm.num_blocks = a->num_blocks;
   prm.block_size = a->block_size;
+  prm.bs_shift = a->block_size == 8 ? 3 : a->block_size == 16 ? 4 : 5;
   prm.bt = a->block_tables;
   prm.bt_ss = a->bt_seq_stride;
   prm.bt_hs = a->bt_head_stride;
