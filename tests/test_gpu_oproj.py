@@ -23,7 +23,7 @@ def _close(got, want_f32, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 8192, 1024), (64, 4096, 512), (1, 64, 64), (77, 640, 1984)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 8192, 1024), (128, 8192, 4096), (64, 4096, 512), (1, 64, 64), (77, 640, 1984)])
 def test_gemm_alone_matches_torch(env, dtype, m, n, k):
     ops, tp_comm = env
     gen = torch.Generator(device="cuda").manual_seed(m + n + k)
