@@ -39,26 +39,58 @@ constexpr int kMergeChunk = 128;  // partitions whose weights are staged at a ti
 template <typename T>
 __device__ __forceinline__ void merge_one(const AttnParams& p, long long slot0, int n, int nparts, long long ooff,
                                           float* wts, int lane) {
-  float M = -INFINITY;
-  for (int k = lane; k < nparts; k += 32) M = fmaxf(M, __ldcg(p.ws_ml + ((slot0 + k) * p.gs + n) * 2));
+  // Everything a warp needs comes from L2, and what costs is the number of DEPENDENT round trips, not the bytes
+  // (this kernel sits between two attention launches): lane k takes partition k's (max, sum) pair in one 8-byte
+  // load, and the accumulators of the first eight partitions are requested at the same time — they do not depend
+  // on the weights.  Items with more than 32 partitions take the general path for the rest.
+  const float* src = p.ws_acc + (slot0 * p.gs + n) * kHeadSize + 4 * lane;
+  const long long stride = (long long)p.gs * kHeadSize;
+  float2 ml0 = make_float2(-INFINITY, 0.f);
+  if (lane < nparts) ml0 = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ((slot0 + lane) * p.gs + n) * 2));
+  constexpr int kPre = 8;
+  float4 pre[kPre];
+#pragma unroll
+  for (int k = 0; k < kPre; ++k)
+    if (k < nparts) pre[k] = __ldcg(reinterpret_cast<const float4*>(src + k * stride));
+  float M = ml0.x;
+  for (int k = lane + 32; k < nparts; k += 32) M = fmaxf(M, __ldcg(p.ws_ml + ((slot0 + k) * p.gs + n) * 2));
   M = warp_max(M);
-  float lsum = 0.f;
-  for (int k = lane; k < nparts; k += 32) {
+  float lsum = ml0.y * __expf(ml0.x - M);  // lanes past nparts: 0 * exp(-inf) = 0
+  for (int k = lane + 32; k < nparts; k += 32) {
     const long long r = (slot0 + k) * p.gs + n;
     lsum += __ldcg(p.ws_ml + r * 2 + 1) * __expf(__ldcg(p.ws_ml + r * 2) - M);
   }
   lsum = warp_sum(lsum);
   const float inv = 1.f / lsum;
+  const float w_lane = __expf(ml0.x - M) * inv;  // weight of partition `lane`
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k0 = 0; k0 < nparts; k0 += kMergeChunk) {
+  const int head = min(nparts, 32);
+#pragma unroll
+  for (int k = 0; k < kPre; ++k) {
+    const float w = __shfl_sync(0xffffffffu, w_lane, k);
+    if (k < head) {
+      acc.x = fmaf(w, pre[k].x, acc.x);
+      acc.y = fmaf(w, pre[k].y, acc.y);
+      acc.z = fmaf(w, pre[k].z, acc.z);
+      acc.w = fmaf(w, pre[k].w, acc.w);
+    }
+  }
+#pragma unroll 8
+  for (int k = kPre; k < head; ++k) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(src + k * stride));
+    const float w = __shfl_sync(0xffffffffu, w_lane, k);
+    acc.x = fmaf(w, a.x, acc.x);
+    acc.y = fmaf(w, a.y, acc.y);
+    acc.z = fmaf(w, a.z, acc.z);
+    acc.w = fmaf(w, a.w, acc.w);
+  }
+  for (int k0 = 32; k0 < nparts; k0 += kMergeChunk) {
     const int cnt = min(kMergeChunk, nparts - k0);
     for (int k = lane; k < cnt; k += 32) wts[k] = __expf(__ldcg(p.ws_ml + ((slot0 + k0 + k) * p.gs + n) * 2) - M) * inv;
     __syncwarp();
-    const float* src = p.ws_acc + ((slot0 + k0) * p.gs + n) * kHeadSize + 4 * lane;
-    const long long stride = (long long)p.gs * kHeadSize;
 #pragma unroll 8
     for (int k = 0; k < cnt; ++k) {
-      const float4 a = __ldcg(reinterpret_cast<const float4*>(src + k * stride));
+      const float4 a = __ldcg(reinterpret_cast<const float4*>(src + (k0 + k) * stride));
       const float w = wts[k];
       acc.x = fmaf(w, a.x, acc.x);
       acc.y = fmaf(w, a.y, acc.y);
@@ -541,10 +573,12 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
   __shared__ float wts[kMergeWarps][kMergeChunk];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int P = p.pb * BS;
-  // This kernel reads nothing before its wait, so the kernel behind it may be scheduled at once: every
-  // kernel of this library waits for its predecessors itself before it touches what they write.
+  // The kernel behind this one may be scheduled at once: every kernel of this library waits for its predecessors
+  // itself before it touches what they write.  Ahead of its own wait this kernel reads at most the launch's index
+  // data (context lengths, head mappings), and only when the caller has said that the kernels ahead do not write it.
   griddep_launch_dependents();
-  griddep_wait();
+  const bool early = (p.flags & MUX_ATTN_EARLY_KV) != 0;  // index data is not written by the kernels just ahead
+  if (!early) griddep_wait();
   const long long unit = (long long)blockIdx.x * kMergeWarps + warp;
   if (unit >= p.num_items * p.head_tiles * p.gs) return;
   const int n = (int)(unit % p.gs);
@@ -560,6 +594,7 @@ paged_attn_merge_kernel(const __grid_constant__ AttnParams p) {
   resolve_heads<MIXED>(p, d, item, htile, info, lane);
   __syncwarp();
   if (n >= info->geff) return;
+  if (early) griddep_wait();  // the partial results and `out` belong to the attention kernel ahead
   const long long slot0 = ((long long)item * p.head_tiles + htile) * p.max_parts;
   merge_one<T>(p, slot0, n, nparts, info->ooff[n], wts[warp], lane);
 }
