@@ -42,6 +42,11 @@ constexpr int kBK = 64;                  // k elements per stage: one 128-byte s
 constexpr int kABytes = kBM * 128;       // 16 KiB
 constexpr int kBBytes = kBN * 128;       // 8 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
+// One ring of 8 (A + W) stages.  Measured alternatives on B200 (m 128, n 8192, k 4096), all slower or equal: separate A
+// and W rings with their own barriers (two waits and two commits per k-block in the issuing thread: +20 %), fewer A
+// and more W stages (6 x 12 ... 4 x 16: the A boxes, although they hit L2, see 2-4 us of latency under this load
+// like the W boxes from DRAM), every CTA starting at a different k-block (no hot spot to spread), weights repacked
+// into contiguous 8 KiB pieces fetched by one bulk copy each (the row-segment access pattern is not the limit).
 constexpr int kStages = 8;
 constexpr int kThreads = 192;            // warps 0-3 epilogue (one thread per row), 4 TMA producer, 5 MMA issuer
 constexpr int kProdWarp = 4, kMmaWarp = 5;
@@ -246,6 +251,8 @@ oproj_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a0, const __grid_
       constexpr uint32_t idesc = instr_desc(fmt, kBN);
       for (int kb = 0; kb < nkb; ++kb) {
         const int st = kb % kStages;
+        // (the wait tests the phase before it suspends: the ring runs ahead of this thread, and a suspended wait costs
+        // a few hundred cycles of wake-up even when the phase is already complete — 18 % of this GEMM's time)
         mbar_wait_sleepy(bar(FULL + st), (uint32_t)(kb / kStages) & 1u, p.status, MUX_DEV_WAIT_TIMEOUT);
         tc_fence_after();
         const uint64_t dA = smem_desc(raw + st * kStageBytes);

@@ -55,6 +55,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase: for a thread that usually finds the phase complete (an MMA issuer behind a deep
+// ring) and cannot afford the wake-up latency of a suspended wait on every pass of its loop.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  When the limit runs out the caller's status word gets
 // `timeout_bit` and the wait returns as if it had succeeded, so that every
 // later barrier of the CTA is still reached and the kernel ends; the result of
@@ -95,6 +109,9 @@ constexpr uint32_t kSleepyLimit = 1u << 18;  // x 2 us: the same order of patien
 
 __device__ __forceinline__ void mbar_wait_sleepy(uint32_t bar, uint32_t parity, unsigned* status,
                                                  unsigned timeout_bit) {
+  // A suspended wait costs a few hundred cycles of wake-up even when the phase is already complete (measured:
+  // 250-450 cycles on B200), and an issuing thread behind a deep ring mostly finds it complete: test first.
+  if (mbar_test_wait(bar, parity)) return;
   for (uint32_t i = 0; i < kSleepyLimit; ++i) {
     if (mbar_try_wait_hint(bar, parity, kSleepyHintNs)) return;
     if ((i & 15u) == 15u && (*reinterpret_cast<volatile unsigned*>(status) & timeout_bit)) return;
