@@ -80,6 +80,7 @@ constexpr uint32_t kWaitRecheck = 1u << 10;
 
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, unsigned* status,
                                           unsigned timeout_bit, uint32_t limit = kWaitLimit) {
+  if (mbar_test_wait(bar, parity)) return;  // usually complete behind a ring: no (potentially suspending) try_wait then
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return;
     if ((i & (kWaitRecheck - 1)) == kWaitRecheck - 1 &&
