@@ -101,6 +101,45 @@ def two_shot(bufs, r, c, calls, out, parity_areas=True):
         yield
 
 
+def owners(bufs, r, c, calls, out, parity_areas=True):
+    """The exchange of the fused o_proj kernel in its tile-owner form (muxserve_b200/csrc/oproj_allreduce.cu): `c` is
+    the output tile, its owner rank is c mod world; the owner's flag array `done` has one entry per tile."""
+    world = len(bufs)
+    my = bufs[r]
+    owner = c % world
+    for _ in range(calls):
+        e = my.epoch[c] + 1
+        par = e & 1 if parity_areas else 0
+        bufs[owner].data[(par, "a", r, c)] = (e, value(r, c, e))   # my partial tile -> the owner's area [r]
+        yield
+        bufs[owner].ready[r][c] = e
+        yield
+        if owner == r:
+            while not all(my.ready[q][c] >= e for q in range(world)):
+                yield
+            total = 0
+            for q in range(world):
+                tag, v = my.data[(par, "a", q, c)]
+                if tag != e:
+                    raise Violation(f"owner {r} tile {c} epoch {e}: partial of rank {q} carries epoch {tag}")
+                total += v
+                yield
+            for q in range(world):                                  # the sum goes where the owner's own partial lay
+                bufs[q].data[(par, "a", r, c)] = (e, total)
+                yield
+            for q in range(world):
+                bufs[q].done[0][c] = e
+                yield
+        while my.done[0][c] < e:
+            yield
+        tag, v = my.data[(par, "a", owner, c)]
+        if tag != e:
+            raise Violation(f"rank {r} tile {c} epoch {e}: the owner's sum carries epoch {tag}")
+        out[r][c].append(v)
+        my.epoch[c] = e
+        yield
+
+
 def run(proto, world, ctas, calls, seed, parity_areas=True, bias=None):
     rng = random.Random(seed)
     bufs = [Buffer(world, ctas) for _ in range(world)]
@@ -153,3 +192,14 @@ def test_without_alternating_areas_the_same_check_catches_the_overwrite():
         except Violation:
             caught += 1
     assert caught > 0, "the model never produced the overwrite it is meant to detect"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_o_proj_owner_exchange_every_read_sees_its_own_epoch(world):
+    calls, tiles = 4, 5          # more tiles than some worlds have ranks, fewer than others: every owner pattern
+    for seed in range(30):
+        out = run(owners, world, tiles, calls, seed, bias=seed % world if seed % 2 == 0 else None)
+        for c in range(tiles):
+            want = [sum(value(q, c, e) for q in range(world)) for e in range(1, calls + 1)]
+            for r in range(world):
+                assert out[r][c] == want
